@@ -1,0 +1,136 @@
+/*
+ * ptxb200 -- C ABI of the sm_100a (B200) native library for the one hot path of
+ * jool-space/PTX.jl: the tcgen05 flash-attention forward kernel and the
+ * tcgen05 bf16 GEMM it is built from.
+ *
+ * Everything here is plain C: raw device pointers, ints and a CUDA stream
+ * handle passed as void* (a cudaStream_t / CUstream; NULL = the legacy default
+ * stream). No torch or C++ types cross this boundary.
+ *
+ * Conventions shared by every entry point
+ *   - Work is enqueued asynchronously on `stream`, on the CUDA device that is
+ *     current in the calling thread. The caller owns every buffer and keeps it
+ *     alive until the stream has passed the enqueued work (the reference states
+ *     the same ownership rule: src/lib/tensor_map.jl:40-42,173-178,
+ *     bench/flash_attention.jl:38-40).
+ *   - Return value: 0 = enqueued. Negative = the call was rejected on the host
+ *     and nothing was launched (see PTXB200_E_*). Device-side trouble (a bounded
+ *     wait inside a kernel ran out) never traps or hangs; it is recorded in a
+ *     per-device status word that ptxb200_sync_status() returns as a positive
+ *     code (0xB2000000 | site << 8 | aux).
+ *   - All device pointers must be 16-byte aligned (TMA and 128-bit stores).
+ *   - Only compute capability 10.x devices are accepted. There is no CPU or
+ *     library fallback: on any other device the calls return
+ *     PTXB200_E_DEVICE.
+ */
+#ifndef PTXB200_H_
+#define PTXB200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PTXB200_OK 0
+#define PTXB200_E_INVALID (-1)   /* null pointer, non-positive size, bad flag       */
+#define PTXB200_E_SHAPE (-2)     /* shape outside the supported contract           */
+#define PTXB200_E_ALIGN (-3)     /* pointer or leading dimension not 16-B aligned   */
+#define PTXB200_E_CUDA (-4)      /* a CUDA runtime call failed (see ptxb200_last_cuda_error) */
+#define PTXB200_E_DRIVER (-5)    /* cuTensorMapEncodeTiled unavailable or failed    */
+#define PTXB200_E_DEVICE (-6)    /* current device is not compute capability 10.x   */
+#define PTXB200_E_CAPACITY (-7)  /* request exceeds a fixed, documented capacity    */
+
+/* gemm_bf16 flags */
+#define PTXB200_GEMM_F32_OUT 0x1u /* write C as fp32 (the reference kernel's output type) */
+
+/* fa_fwd_bf16 flags */
+#define PTXB200_FA_NO_LAZY_RESCALE 0x1u /* rescale O on every row-max increase (no 2^8 slack) */
+
+/* Library version: major*10000 + minor*100 + patch. */
+int ptxb200_version(void);
+
+/* Human-readable text for a return code (negative host codes and positive
+ * device status codes). Never returns NULL. */
+const char* ptxb200_strerror(int code);
+
+/* Text of the last CUDA runtime / driver error seen by the calling thread inside
+ * this library ("" if none). */
+const char* ptxb200_last_cuda_error(void);
+
+/*
+ * C[M,N] = A[M,K] * B[K,N], bf16 operands, fp32 accumulation in tensor memory,
+ * bf16 (default) or fp32 (PTXB200_GEMM_F32_OUT) output.
+ *
+ *   A   [M,K] row-major bf16 (K contiguous)
+ *   Bt  B stored column-major, i.e. B transposed: [N,K] row-major bf16
+ *   C   [M,N] row-major with leading dimension ldc (elements), ldc >= N
+ *
+ * Shape contract: M % 128 == 0, N % 128 == 0, K % 64 == 0, all > 0;
+ * ldc * sizeof(element) % 16 == 0.
+ *
+ * Replaces the reference's _run_ghb launch of _ghb_gemm_kernel! /
+ * _ghb_persistent_kernel! (test/gpu/blackwell/gemm_highperf_blackwell.jl:69-199,
+ * 230-269, 317-468): same operand packing (A K-fast, B as [N,K] K-fast), same
+ * fp32 accumulation; the reference writes fp32 only.
+ */
+int gemm_bf16(void* C, const void* A, const void* Bt, int M, int N, int K, int ldc,
+              unsigned flags, void* stream);
+
+/*
+ * O = softmax(Q K^T * sm_scale [+ causal mask]) V, row-wise, per (batch, head).
+ *
+ *   Q, K, V, O  [B,H,S,D] row-major bf16 == a 2-D (B*H*S, D) matrix, D contiguous
+ *               (the reference's layout: flash_attention_defs.jl:90, 979-986)
+ *   D           64 or 128
+ *   S           multiple of 256
+ *   causal      0: every key; 1: key j is kept for query i iff j <= i
+ *               (mask convention of test/gpu/ampere/flash_attention.jl:176-186)
+ *   dbg         NULL, or 64 uint32 words on the device that receive per-role
+ *               progress counters of CTA 0 (diagnostics only)
+ *
+ * Scores are accumulated in fp32, the softmax runs in fp32 with the row maximum
+ * subtracted, P is rounded to bf16 for the second product, O is accumulated in
+ * fp32 and rounded once to bf16.
+ *
+ * Replaces the reference's fab_setup launch closure of fab_kernel!
+ * (bench/flash_attention.jl:41-85; test/gpu/blackwell/flash_attention_defs.jl:
+ * 621-961), which covers D = 128, non-causal only.
+ */
+int fa_fwd_bf16(void* O, const void* Q, const void* K, const void* V, int B, int H, int S, int D,
+                float sm_scale, int causal, unsigned flags, void* dbg, void* stream);
+
+/*
+ * Synchronise `stream`, then return and clear the current device's status word:
+ * 0 if every kernel enqueued through this library since the last call ran to
+ * completion normally, a positive code if a bounded device-side wait ran out
+ * (the affected outputs are then invalid), PTXB200_E_CUDA if the stream itself
+ * reports an error. Replaces the reference's beacon buffer read-back
+ * (flash_attention_defs.jl:224-267, 989-998).
+ */
+int ptxb200_sync_status(void* stream);
+
+/*
+ * Bring-up probes with known answers, restating the reference's single-
+ * instruction runtime tests (test/gpu/blackwell/tcgen05_roundtrip.jl:22-88,
+ * tcgen05_mma_probe.jl:39-131, tcgen05_b128_probe.jl). `which`:
+ *   0  TMEM store -> load identity. out: 128*128 uint32, out[r*128+c] must equal
+ *      (r << 16 | c) ^ 0x5A5A0000.
+ *   1  one attention tile, D = 128:  out_s = Q K^T (128x128 fp32) and
+ *      out_o = P V (128xD fp32) with P (bf16, 128x128) read from tensor memory
+ *      and V as an MN-major shared-memory operand.
+ *   2  the same with D = 64.
+ * For 1 and 2: q,k,v are (128, D) bf16, p is (128,128) bf16, all row-major.
+ * Unused pointers may be NULL for probe 0.
+ */
+int ptxb200_selftest(int which, void* out_s, void* out_o, const void* q, const void* k,
+                     const void* v, const void* p, void* stream);
+
+/* Release the per-device workspaces this library allocated. Optional. */
+int ptxb200_shutdown(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PTXB200_H_ */

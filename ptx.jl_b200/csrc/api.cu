@@ -1,0 +1,215 @@
+// C-ABI entry points and host plumbing of libptxb200. See include/ptxb200.h for
+// the contract of each call.
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <vector>
+
+#include "host_common.h"
+
+namespace ptxb200 {
+
+// ---------------------------------------------------------------------------
+// error text
+// ---------------------------------------------------------------------------
+static thread_local char g_err[512] = "";
+
+void set_cuda_error(const char* what, cudaError_t e) {
+  snprintf(g_err, sizeof(g_err), "%s: %s (%s)", what, cudaGetErrorName(e), cudaGetErrorString(e));
+}
+void set_error_text(const char* what) { snprintf(g_err, sizeof(g_err), "%s", what); }
+const char* get_cuda_error() { return g_err; }
+
+// ---------------------------------------------------------------------------
+// per-device contexts
+// ---------------------------------------------------------------------------
+static std::mutex g_mu;
+static std::vector<DeviceCtx*> g_ctx;  // indexed by device ordinal
+
+int current_ctx(DeviceCtx** out) {
+  int dev = -1;
+  PTXB200_CUDA_TRY(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> lock(g_mu);
+  if ((int)g_ctx.size() <= dev) g_ctx.resize(dev + 1, nullptr);
+  if (g_ctx[dev] == nullptr) {
+    DeviceCtx c;
+    c.device = dev;
+    PTXB200_CUDA_TRY(cudaDeviceGetAttribute(&c.sm_count, cudaDevAttrMultiProcessorCount, dev));
+    PTXB200_CUDA_TRY(cudaDeviceGetAttribute(&c.cc_major, cudaDevAttrComputeCapabilityMajor, dev));
+    PTXB200_CUDA_TRY(cudaDeviceGetAttribute(&c.cc_minor, cudaDevAttrComputeCapabilityMinor, dev));
+    if (c.cc_major != 10) {
+      set_error_text("current device is not compute capability 10.x (sm_100a code only)");
+      return PTXB200_E_DEVICE;
+    }
+    PTXB200_CUDA_TRY(cudaMalloc((void**)&c.workspace, kWsWords * sizeof(uint32_t)));
+    PTXB200_CUDA_TRY(cudaMemset(c.workspace, 0, kWsWords * sizeof(uint32_t)));
+    g_ctx[dev] = new DeviceCtx(c);
+  }
+  *out = g_ctx[dev];
+  return PTXB200_OK;
+}
+
+int release_all_ctx() {
+  std::lock_guard<std::mutex> lock(g_mu);
+  int prev = -1;
+  cudaGetDevice(&prev);
+  for (DeviceCtx*& c : g_ctx) {
+    if (c == nullptr) continue;
+    if (cudaSetDevice(c->device) == cudaSuccess && c->workspace != nullptr) cudaFree(c->workspace);
+    delete c;
+    c = nullptr;
+  }
+  if (prev >= 0) cudaSetDevice(prev);
+  return PTXB200_OK;
+}
+
+// ---------------------------------------------------------------------------
+// tensor maps
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = []() -> EncodeTiledFn {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q);
+    if (e != cudaSuccess || q != cudaDriverEntryPointSuccess) return nullptr;
+    return (EncodeTiledFn)p;
+  }();
+  return fn;
+}
+
+int encode_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols,
+                        uint64_t row_pitch_bytes, uint32_t box_rows, uint32_t box_cols) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) {
+    set_error_text("cuTensorMapEncodeTiled: driver entry point not found");
+    return PTXB200_E_DRIVER;
+  }
+  cuuint64_t dims[2] = {cols, rows};               // innermost first
+  cuuint64_t strides[1] = {row_pitch_bytes};       // stride of dim 1; dim 0 is implicit
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    snprintf(g_err, sizeof(g_err), "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return PTXB200_E_DRIVER;
+  }
+  return PTXB200_OK;
+}
+
+}  // namespace ptxb200
+
+using namespace ptxb200;
+
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+extern "C" {
+
+int ptxb200_version(void) { return 100; /* 0.1.0 */ }
+
+const char* ptxb200_last_cuda_error(void) { return get_cuda_error(); }
+
+const char* ptxb200_strerror(int code) {
+  switch (code) {
+    case PTXB200_OK: return "ok";
+    case PTXB200_E_INVALID: return "invalid argument (null pointer, non-positive size or unknown flag)";
+    case PTXB200_E_SHAPE: return "shape outside the supported contract";
+    case PTXB200_E_ALIGN: return "pointer or leading dimension is not 16-byte aligned";
+    case PTXB200_E_CUDA: return "CUDA runtime error (see ptxb200_last_cuda_error)";
+    case PTXB200_E_DRIVER: return "cuTensorMapEncodeTiled unavailable or failed";
+    case PTXB200_E_DEVICE: return "current device is not compute capability 10.x";
+    case PTXB200_E_CAPACITY: return "request exceeds a fixed capacity of this entry point";
+    default: break;
+  }
+  if (code > 0 && ((uint32_t)code & 0xFF000000u) == 0xB2000000u) {
+    static thread_local char buf[160];
+    static const char* const sites[] = {
+        "?",            "gemm:empty",    "gemm:full",    "gemm:acc_empty", "gemm:acc_full",
+        "fa:load.q_free", "fa:load.kv_free", "fa:mma.q_full", "fa:mma.kv_full", "fa:mma.p_full",
+        "fa:mma.o_ready", "fa:softmax.s_full", "fa:corr.alpha", "fa:corr.l_ready",
+        "fa:corr.o_done", "probe",
+    };
+    unsigned site = ((unsigned)code >> 8) & 0xFFu;
+    const char* name = site < sizeof(sites) / sizeof(sites[0]) ? sites[site] : "?";
+    snprintf(buf, sizeof(buf),
+             "device-side bounded wait ran out at site %u (%s), cta%%128=%u, parity=%u; outputs "
+             "of that launch are invalid",
+             site, name, ((unsigned)code >> 1) & 0x7Fu, (unsigned)code & 1u);
+    return buf;
+  }
+  return "unknown code";
+}
+
+int gemm_bf16(void* C, const void* A, const void* Bt, int M, int N, int K, int ldc, unsigned flags,
+              void* stream) {
+  if (C == nullptr || A == nullptr || Bt == nullptr) return PTXB200_E_INVALID;
+  if (M <= 0 || N <= 0 || K <= 0 || ldc < N) return PTXB200_E_INVALID;
+  if (flags & ~PTXB200_GEMM_F32_OUT) return PTXB200_E_INVALID;
+  if (M % 128 != 0 || N % 128 != 0 || K % 64 != 0) return PTXB200_E_SHAPE;
+  const size_t esz = (flags & PTXB200_GEMM_F32_OUT) ? 4 : 2;
+  if (!aligned16(C) || !aligned16(A) || !aligned16(Bt) || ((size_t)ldc * esz) % 16 != 0)
+    return PTXB200_E_ALIGN;
+  DeviceCtx* ctx = nullptr;
+  int rc = current_ctx(&ctx);
+  if (rc != PTXB200_OK) return rc;
+  return launch_gemm(*ctx, C, A, Bt, M, N, K, ldc, flags, (cudaStream_t)stream);
+}
+
+int fa_fwd_bf16(void* O, const void* Q, const void* K, const void* V, int B, int H, int S, int D,
+                float sm_scale, int causal, unsigned flags, void* dbg, void* stream) {
+  if (O == nullptr || Q == nullptr || K == nullptr || V == nullptr) return PTXB200_E_INVALID;
+  if (B <= 0 || H <= 0 || S <= 0 || D <= 0) return PTXB200_E_INVALID;
+  if (causal != 0 && causal != 1) return PTXB200_E_INVALID;
+  if (flags & ~PTXB200_FA_NO_LAZY_RESCALE) return PTXB200_E_INVALID;
+  if (!(sm_scale > 0.0f) || !(sm_scale < 1e30f)) return PTXB200_E_INVALID;
+  if ((D != 64 && D != 128) || S % 256 != 0) return PTXB200_E_SHAPE;
+  if ((long long)B * H * S >= (1ll << 31)) return PTXB200_E_SHAPE;
+  if (!aligned16(O) || !aligned16(Q) || !aligned16(K) || !aligned16(V)) return PTXB200_E_ALIGN;
+  if (dbg != nullptr && !aligned16(dbg)) return PTXB200_E_ALIGN;
+  DeviceCtx* ctx = nullptr;
+  int rc = current_ctx(&ctx);
+  if (rc != PTXB200_OK) return rc;
+  return launch_fa_fwd(*ctx, O, Q, K, V, B, H, S, D, sm_scale, causal, flags, dbg,
+                       ctx->workspace + kWsStatus, (cudaStream_t)stream);
+}
+
+int ptxb200_sync_status(void* stream) {
+  DeviceCtx* ctx = nullptr;
+  int rc = current_ctx(&ctx);
+  if (rc != PTXB200_OK) return rc;
+  cudaStream_t s = (cudaStream_t)stream;
+  uint32_t word = 0;
+  PTXB200_CUDA_TRY(cudaMemcpyAsync(&word, ctx->workspace + kWsStatus, sizeof(word),
+                                   cudaMemcpyDeviceToHost, s));
+  PTXB200_CUDA_TRY(cudaStreamSynchronize(s));
+  if (word != 0) {
+    PTXB200_CUDA_TRY(cudaMemsetAsync(ctx->workspace + kWsStatus, 0, sizeof(word), s));
+    PTXB200_CUDA_TRY(cudaStreamSynchronize(s));
+  }
+  return (int)word;
+}
+
+int ptxb200_selftest(int which, void* out_s, void* out_o, const void* q, const void* k,
+                     const void* v, const void* p, void* stream) {
+  if (which < 0 || which > 2) return PTXB200_E_INVALID;
+  if (out_s == nullptr) return PTXB200_E_INVALID;
+  if (which != 0 && (out_o == nullptr || q == nullptr || k == nullptr || v == nullptr || p == nullptr))
+    return PTXB200_E_INVALID;
+  if (!aligned16(out_s) || !aligned16(out_o) || !aligned16(q) || !aligned16(k) || !aligned16(v) ||
+      !aligned16(p))
+    return PTXB200_E_ALIGN;
+  DeviceCtx* ctx = nullptr;
+  int rc = current_ctx(&ctx);
+  if (rc != PTXB200_OK) return rc;
+  return launch_selftest(*ctx, which, out_s, out_o, q, k, v, p, (cudaStream_t)stream);
+}
+
+int ptxb200_shutdown(void) { return release_all_ctx(); }
+
+}  // extern "C"

@@ -1,0 +1,499 @@
+// fa_fwd_bf16: O = softmax(Q K^T * scale [+ causal mask]) V on sm_100a.
+//
+// The reference kernel for this path is fab_kernel!
+// (test/gpu/blackwell/flash_attention_defs.jl:621-961): head dim 128, non-causal
+// only, 256 query rows per work item as two 128-row stages, S and O in tensor
+// memory, P written back over S as bf16 and consumed from tensor memory by the
+// second product, a "stale basis" softmax that starts from basis 0 and defers the
+// row-max decision by one tile.
+//
+// This kernel keeps the tensor-memory residency (it is what the hardware wants)
+// but is its own design in what it computes and how the roles talk:
+//   * exact online softmax: every tile's exponentials use a basis that already
+//     includes that tile's row maximum (no basis-0 first tile, so large logits
+//     cannot overflow); O is rescaled only when the maximum grew by more than
+//     2^8 (the slack cancels exactly in the final O / l);
+//   * head dim 64 and 128, causal and non-causal, from one template;
+//   * causal work items skip the key tiles above the diagonal per 128-row stage,
+//     mask only the diagonal tile, and are handed out longest first;
+//   * a protocol of single-producer/single-consumer mbarrier phases in which no
+//     producer can run two phases ahead of its consumer (argued per barrier
+//     below), so no padding commits and no split-by-parity barriers are needed;
+//   * every wait is bounded and reports to a status word.
+//
+// Roles (512 threads): warps 0-3 / 4-7 softmax of stage 0 / 1 (thread = one row),
+// warps 8-11 correction + epilogue, warp 12 MMA issue, warp 13 TMA loads,
+// warps 14-15 idle (they only take part in the register re-split).
+//
+// Tensor memory (512 columns x 128 lanes of 32 bit):
+//   S0 at 0, S1 at 128 (fp32, 128 columns each; P_s overwrites the first 64
+//   columns of S_s as packed bf16), O0 at 256, O1 at 256 + D.
+//
+// Algorithmic work per launch: 4*B*H*S*S*D flop non-causal, 2*B*H*S*S*D causal
+// (softmax excluded; the reference's convention, bench/flash_attention.jl:107-108).
+#include <math.h>
+
+#include "attn_tiles.cuh"
+#include "host_common.h"
+
+namespace ptxb200 {
+namespace {
+
+constexpr int kThreads = 512;
+constexpr int kRegsSoftmax = 184;
+constexpr int kRegsCorrection = 72;
+constexpr int kRegsOther = 72;
+static_assert(256 * kRegsSoftmax + 128 * kRegsCorrection + 128 * kRegsOther <= 65536,
+              "register re-split must fit the register file");
+
+enum : uint32_t {
+  kSiteLoadQFree = 5, kSiteLoadKvFree = 6, kSiteMmaQFull = 7, kSiteMmaKvFull = 8,
+  kSiteMmaPFull = 9, kSiteMmaOReady = 10, kSiteSoftmaxSFull = 11, kSiteCorrAlpha = 12,
+  kSiteCorrLReady = 13, kSiteCorrODone = 14
+};
+
+template <int D>
+struct FaCfg {
+  using T = AttnTile<D>;
+  static constexpr int kSlots = (D == 128) ? 4 : 8;           // K/V ring slots (one tile each)
+  static constexpr int kOffQ = 0;
+  static constexpr int kOffKV = kOffQ + 2 * T::kTileBytes;
+  static constexpr int kOffStats = kOffKV + kSlots * T::kTileBytes;  // alpha[2][128], l[2][128]
+  static constexpr int kOffBars = kOffStats + 4 * 128 * 4;
+  // barrier indices (8 bytes each)
+  static constexpr int kBarQFull = 0;                  // [2]  TMA tx
+  static constexpr int kBarQFree = 2;                  //      tcgen05.commit
+  static constexpr int kBarKvFull = 3;                 // [kSlots] TMA tx
+  static constexpr int kBarKvFree = kBarKvFull + kSlots;   // [kSlots] tcgen05.commit
+  static constexpr int kBarSFull = kBarKvFree + kSlots;    // [2] tcgen05.commit
+  static constexpr int kBarPFull = kBarSFull + 2;      // [2] 128 softmax threads
+  static constexpr int kBarAlpha = kBarPFull + 2;      // [2] 128 softmax threads
+  static constexpr int kBarLReady = kBarAlpha + 2;     // [2] 128 softmax threads
+  static constexpr int kBarOReady = kBarLReady + 2;    // [2] 128 correction threads
+  static constexpr int kBarODone = kBarOReady + 2;     // [2] tcgen05.commit
+  static constexpr int kNumBars = kBarODone + 2;
+  static constexpr int kOffTmemSlot = kOffBars + kNumBars * 8;
+  static constexpr int kOffAbort = kOffTmemSlot + 8;
+  static constexpr int kSmemBytes = kOffAbort + 8 + 1024;  // + slack for manual alignment
+  static constexpr uint32_t kColS = 0;                 // + stage * 128
+  static constexpr uint32_t kColO = 256;               // + stage * D
+};
+
+struct FaParams {
+  __nv_bfloat16* o;
+  int seqlen;        // S
+  int num_mblocks;   // S / 256
+  int bh;            // B * H
+  int total_work;    // num_mblocks * bh
+  float scale_log2;  // sm_scale * log2(e)
+  float rescale_threshold;  // in log2 units of the scaled scores
+  uint32_t* status;
+  uint32_t* dbg;
+};
+
+// Work item -> (m_block, batch*head). Non-causal: m_block fastest, so CTAs that
+// run together share one head's K/V in L2 (flash_attention_defs.jl:80-82).
+// Causal: items sorted by decreasing length (m_block descending, slowest).
+template <bool kCausal>
+__device__ __forceinline__ void decode_item(const FaParams& p, int w, int& mb, int& bh) {
+  if (kCausal) {
+    mb = p.num_mblocks - 1 - w / p.bh;
+    bh = w % p.bh;
+  } else {
+    mb = w % p.num_mblocks;
+    bh = w / p.num_mblocks;
+  }
+}
+// Key tiles each stage of the item visits.
+template <bool kCausal>
+__device__ __forceinline__ void tile_counts(const FaParams& p, int mb, int& nt0, int& nt1) {
+  if (kCausal) {
+    nt0 = 2 * mb + 1;
+    nt1 = 2 * mb + 2;
+  } else {
+    nt0 = nt1 = p.seqlen / kAttnRows;
+  }
+}
+
+template <int D, bool kCausal>
+__global__ void __launch_bounds__(kThreads, 1)
+fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+              const __grid_constant__ CUtensorMap tmap_v, const FaParams p) {
+  using C = FaCfg<D>;
+  using T = AttnTile<D>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - smem_u32(smem_raw));
+
+  const uint32_t q_smem = base + C::kOffQ;
+  const uint32_t kv_smem = base + C::kOffKV;
+  float* stats_alpha = reinterpret_cast<float*>(smem + C::kOffStats);          // [2][128]
+  float* stats_l = stats_alpha + 256;                                          // [2][128]
+  const uint32_t bars = base + C::kOffBars;
+  auto bar = [bars](int idx) -> uint32_t { return bars + 8u * (uint32_t)idx; };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + C::kOffTmemSlot);
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + C::kOffAbort);
+  const WaitCtx wctx{p.status, abort_flag};
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+
+  if (tid == 0) {
+    *abort_flag = 0;
+    mbar_init(bar(C::kBarQFull + 0), 1);
+    mbar_init(bar(C::kBarQFull + 1), 1);
+    mbar_init(bar(C::kBarQFree), 1);
+    for (int s = 0; s < C::kSlots; ++s) {
+      mbar_init(bar(C::kBarKvFull + s), 1);
+      mbar_init(bar(C::kBarKvFree + s), 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar(C::kBarSFull + s), 1);
+      mbar_init(bar(C::kBarPFull + s), 128);
+      mbar_init(bar(C::kBarAlpha + s), 128);
+      mbar_init(bar(C::kBarLReady + s), 128);
+      mbar_init(bar(C::kBarOReady + s), 128);
+      mbar_init(bar(C::kBarODone + s), 1);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 12) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp >= 12) {
+    // =====================================================================
+    // warpgroup 3: TMA loads (warp 13) and MMA issue (warp 12)
+    // =====================================================================
+    setmaxnreg_dec<kRegsOther>();
+    if (warp == 13) {
+      if (elect_one()) {
+        tma_prefetch_desc(&tmap_q);
+        tma_prefetch_desc(&tmap_k);
+        tma_prefetch_desc(&tmap_v);
+        uint32_t kv_it = 0, item_i = 0;
+        auto kv_load = [&](const void* tmap, int row) {
+          const uint32_t s = kv_it % C::kSlots;
+          const uint32_t ph = (kv_it / C::kSlots) & 1u;
+          mbar_wait(bar(C::kBarKvFree + s), ph ^ 1u, wctx, kSiteLoadKvFree);
+          mbar_arrive_expect_tx(bar(C::kBarKvFull + s), T::kTileBytes);
+          T::load(kv_smem + s * T::kTileBytes, tmap, row, bar(C::kBarKvFull + s));
+          ++kv_it;
+        };
+        for (int w = blockIdx.x; w < p.total_work; w += gridDim.x, ++item_i) {
+          int mb, bh, nt0, nt1;
+          decode_item<kCausal>(p, w, mb, bh);
+          tile_counts<kCausal>(p, mb, nt0, nt1);
+          const int kv_row0 = bh * p.seqlen;
+          const int q_row0 = kv_row0 + mb * 2 * kAttnRows;
+          // Q may be overwritten once every S = Q K^T of the previous item has run
+          mbar_wait(bar(C::kBarQFree), (item_i & 1u) ^ 1u, wctx, kSiteLoadQFree);
+          mbar_arrive_expect_tx(bar(C::kBarQFull + 0), T::kTileBytes);
+          T::load(q_smem, &tmap_q, q_row0, bar(C::kBarQFull + 0));
+          kv_load(&tmap_k, kv_row0);
+          mbar_arrive_expect_tx(bar(C::kBarQFull + 1), T::kTileBytes);
+          T::load(q_smem + T::kTileBytes, &tmap_q, q_row0 + kAttnRows, bar(C::kBarQFull + 1));
+          for (int j = 0; j < nt1; ++j) {
+            kv_load(&tmap_v, kv_row0 + j * kAttnRows);
+            if (j + 1 < nt1) kv_load(&tmap_k, kv_row0 + (j + 1) * kAttnRows);
+          }
+        }
+        if (p.dbg != nullptr && blockIdx.x == 0) p.dbg[0] = kv_it;
+      }
+    } else if (warp == 12) {
+      if (elect_one()) {
+        uint32_t kv_it = 0, item_i = 0;
+        uint32_t cnt_pv[2] = {0, 0};   // P*V products issued per stage (p_full and o_ready phases)
+        auto kv_wait = [&]() -> uint32_t {   // returns the ring slot
+          const uint32_t s = kv_it % C::kSlots;
+          const uint32_t ph = (kv_it / C::kSlots) & 1u;
+          mbar_wait(bar(C::kBarKvFull + s), ph, wctx, kSiteMmaKvFull);
+          ++kv_it;
+          return s;
+        };
+        auto qk = [&](int stage, uint32_t kslot) {   // S_stage = Q_stage K^T
+          const uint32_t qa = q_smem + stage * T::kTileBytes;
+          const uint32_t ka = kv_smem + kslot * T::kTileBytes;
+#pragma unroll
+          for (int kk = 0; kk < T::kQKAtoms; ++kk)
+            tc_mma_ss(tmem + C::kColS + stage * 128, T::kmajor_lo(qa, kk), T::kKMajorHi,
+                      T::kmajor_lo(ka, kk), T::kKMajorHi, T::kIdescQK, kk != 0 ? 1u : 0u);
+          tc_commit(bar(C::kBarSFull + stage));
+        };
+        auto pv = [&](int stage, uint32_t vslot, bool accumulate) {   // O_stage (+)= P_stage V
+          const uint32_t va = kv_smem + vslot * T::kTileBytes;
+#pragma unroll
+          for (int kk = 0; kk < T::kPVAtoms; ++kk)
+            tc_mma_ts(tmem + C::kColO + stage * D, T::p_tmem(tmem, C::kColS + stage * 128, kk),
+                      T::v_lo(va, kk), T::kVHi, T::kIdescPV, (accumulate || kk != 0) ? 1u : 0u);
+        };
+        for (int w = blockIdx.x; w < p.total_work; w += gridDim.x, ++item_i) {
+          int mb, bh, nt[2];
+          decode_item<kCausal>(p, w, mb, bh);
+          tile_counts<kCausal>(p, mb, nt[0], nt[1]);
+          const int nt_max = nt[1];
+          const uint32_t qph = item_i & 1u;
+          mbar_wait(bar(C::kBarQFull + 0), qph, wctx, kSiteMmaQFull);
+          const uint32_t k0 = kv_wait();
+          tc_fence_after();
+          qk(0, k0);
+          mbar_wait(bar(C::kBarQFull + 1), qph, wctx, kSiteMmaQFull);
+          tc_fence_after();
+          qk(1, k0);
+          tc_commit(bar(C::kBarKvFree + k0));
+          if (nt_max == 1) tc_commit(bar(C::kBarQFree));
+          for (int j = 0; j < nt_max; ++j) {
+            const uint32_t vslot = kv_wait();
+            const bool has_next = (j + 1 < nt_max);
+            uint32_t kslot = 0;
+            if (has_next) kslot = kv_wait();
+#pragma unroll
+            for (int s = 0; s < 2; ++s) {
+              if (j < nt[s]) {
+                mbar_wait(bar(C::kBarPFull + s), cnt_pv[s] & 1u, wctx, kSiteMmaPFull);
+                mbar_wait(bar(C::kBarOReady + s), cnt_pv[s] & 1u, wctx, kSiteMmaOReady);
+                ++cnt_pv[s];
+                tc_fence_after();
+                pv(s, vslot, j > 0);
+                if (j + 1 < nt[s]) qk(s, kslot);
+                else tc_commit(bar(C::kBarODone + s));
+              }
+            }
+            tc_commit(bar(C::kBarKvFree + vslot));
+            if (has_next) tc_commit(bar(C::kBarKvFree + kslot));
+            if (j + 2 == nt_max) tc_commit(bar(C::kBarQFree));   // last Q K^T issued
+          }
+        }
+        if (p.dbg != nullptr && blockIdx.x == 0) {
+          p.dbg[1] = kv_it;
+          p.dbg[2] = cnt_pv[0];
+          p.dbg[3] = cnt_pv[1];
+        }
+      }
+    }
+  } else if (warp < 8) {
+    // =====================================================================
+    // softmax: warpgroup `stage` owns the 128 rows of that stage; one row
+    // per thread, the whole 128-column tile of scores in registers.
+    // =====================================================================
+    setmaxnreg_inc<kRegsSoftmax>();
+    const int stage = warp >> 2;
+    const int row = tid & 127;
+    const uint32_t t_row = tmem_addr(tmem, (warp & 3) * 32, C::kColS + stage * 128);
+    const float scale_log2 = p.scale_log2;
+    uint32_t cnt_s = 0;
+    for (int w = blockIdx.x; w < p.total_work; w += gridDim.x) {
+      int mb, bh, nt[2];
+      decode_item<kCausal>(p, w, mb, bh);
+      tile_counts<kCausal>(p, mb, nt[0], nt[1]);
+      const int ntiles = nt[stage];
+      float m_run = -INFINITY;
+      float l_run = 0.0f;
+#pragma unroll 1
+      for (int j = 0; j < ntiles; ++j) {
+        mbar_wait(bar(C::kBarSFull + stage), cnt_s & 1u, wctx, kSiteSoftmaxSFull);
+        ++cnt_s;
+        tc_fence_after();
+        uint32_t v[4][32];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tmem_ld32(t_row + c * 32, v[c]);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tc_wait_ld_bind(v[c]);
+
+        if (kCausal && j == ntiles - 1) {
+          // diagonal tile: key (local) column i is kept iff i <= row
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (c * 32 + i > row) v[c][i] = 0xFF800000u;  // -inf
+        }
+
+        float mx[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          float m = fmaxf(__uint_as_float(v[c][0]), __uint_as_float(v[c][1]));
+#pragma unroll
+          for (int i = 2; i < 32; i += 2)
+            m = max3(m, __uint_as_float(v[c][i]), __uint_as_float(v[c][i + 1]));
+          mx[c] = m;
+        }
+        const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+
+        if (j == 0) {
+          m_run = m_tile;
+        } else {
+          float alpha = 1.0f;
+          const float m_new = fmaxf(m_run, m_tile);
+          if ((m_new - m_run) * scale_log2 > p.rescale_threshold) {
+            alpha = ex2_approx((m_run - m_new) * scale_log2);
+            m_run = m_new;
+          }
+          stats_alpha[stage * 128 + row] = alpha;
+          mbar_arrive(bar(C::kBarAlpha + stage));
+          l_run *= alpha;
+        }
+
+        const float neg = -m_run * scale_log2;
+        float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float e0 = ex2_approx(fmaf(__uint_as_float(v[c][2 * i]), scale_log2, neg));
+            const float e1 = ex2_approx(fmaf(__uint_as_float(v[c][2 * i + 1]), scale_log2, neg));
+            sum[i & 3] += e0 + e1;
+            pk[i] = pack_bf16x2(e0, e1);
+          }
+          tmem_st16(t_row + c * 16, pk);
+        }
+        tc_wait_st();
+        tc_fence_before();
+        mbar_arrive(bar(C::kBarPFull + stage));
+        l_run += (sum[0] + sum[1]) + (sum[2] + sum[3]);
+      }
+      stats_l[stage * 128 + row] = l_run;
+      mbar_arrive(bar(C::kBarLReady + stage));
+    }
+    if (p.dbg != nullptr && blockIdx.x == 0 && row == 0) p.dbg[6 + stage] = cnt_s;
+  } else {
+    // =====================================================================
+    // correction (rescale O when a row maximum moved) + epilogue
+    // =====================================================================
+    setmaxnreg_dec<kRegsCorrection>();
+    const int row = tid & 127;
+    const uint32_t t_lane = tmem_addr(tmem, (warp & 3) * 32, 0);
+    mbar_arrive(bar(C::kBarOReady + 0));   // O is free for the first item
+    mbar_arrive(bar(C::kBarOReady + 1));
+    uint32_t cnt_a[2] = {0, 0};
+    uint32_t item_i = 0;
+    for (int w = blockIdx.x; w < p.total_work; w += gridDim.x, ++item_i) {
+      int mb, bh, nt[2];
+      decode_item<kCausal>(p, w, mb, bh);
+      tile_counts<kCausal>(p, mb, nt[0], nt[1]);
+      const int nt_max = nt[1];
+#pragma unroll 1
+      for (int j = 1; j < nt_max; ++j) {
+#pragma unroll
+        for (int s = 0; s < 2; ++s) {
+          if (j < nt[s]) {
+            mbar_wait(bar(C::kBarAlpha + s), cnt_a[s] & 1u, wctx, kSiteCorrAlpha);
+            ++cnt_a[s];
+            const float alpha = stats_alpha[s * 128 + row];
+            if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+              tc_fence_after();
+#pragma unroll 1
+              for (int c = 0; c < D / 32; ++c) {
+                uint32_t o[32];
+                const uint32_t a = t_lane + C::kColO + s * D + c * 32;
+                tmem_ld32(a, o);
+                tc_wait_ld_bind(o);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                tmem_st32(a, o);
+              }
+              tc_wait_st();
+            }
+            tc_fence_before();
+            mbar_arrive(bar(C::kBarOReady + s));
+          }
+        }
+      }
+      // ---- epilogue: O / l -> bf16 -> global ----
+      const int q_row0 = bh * p.seqlen + mb * 2 * kAttnRows;
+#pragma unroll
+      for (int s = 0; s < 2; ++s) {
+        mbar_wait(bar(C::kBarODone + s), item_i & 1u, wctx, kSiteCorrODone);
+        mbar_wait(bar(C::kBarLReady + s), item_i & 1u, wctx, kSiteCorrLReady);
+        tc_fence_after();
+        const float inv_l = 1.0f / stats_l[s * 128 + row];
+        __nv_bfloat16* dst = p.o + (size_t)(q_row0 + s * kAttnRows + row) * D;
+#pragma unroll 1
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld32(t_lane + C::kColO + s * D + c * 32, o);
+          tc_wait_ld_bind(o);
+          if (c == D / 32 - 1) {
+            // last read of O_s: the next item may overwrite it
+            tc_fence_before();
+            mbar_arrive(bar(C::kBarOReady + s));
+          }
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const uint32_t p0 = pack_bf16x2(__uint_as_float(o[8 * i + 0]) * inv_l, __uint_as_float(o[8 * i + 1]) * inv_l);
+            const uint32_t p1 = pack_bf16x2(__uint_as_float(o[8 * i + 2]) * inv_l, __uint_as_float(o[8 * i + 3]) * inv_l);
+            const uint32_t p2 = pack_bf16x2(__uint_as_float(o[8 * i + 4]) * inv_l, __uint_as_float(o[8 * i + 5]) * inv_l);
+            const uint32_t p3 = pack_bf16x2(__uint_as_float(o[8 * i + 6]) * inv_l, __uint_as_float(o[8 * i + 7]) * inv_l);
+            st_global_v4(dst + c * 32 + 8 * i, p0, p1, p2, p3);
+          }
+        }
+      }
+    }
+    if (p.dbg != nullptr && blockIdx.x == 0 && row == 0) {
+      p.dbg[8] = cnt_a[0];
+      p.dbg[9] = cnt_a[1];
+      p.dbg[10] = item_i;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 12) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+template <int D, bool kCausal>
+int launch_variant(const DeviceCtx& ctx, const CUtensorMap& tq, const CUtensorMap& tk,
+                   const CUtensorMap& tv, const FaParams& p, cudaStream_t stream) {
+  using C = FaCfg<D>;
+  static bool attr_done[64] = {false};
+  if (!attr_done[ctx.device & 63]) {
+    PTXB200_CUDA_TRY(cudaFuncSetAttribute(fa_fwd_kernel<D, kCausal>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          C::kSmemBytes));
+    attr_done[ctx.device & 63] = true;
+  }
+  const int grid = p.total_work < ctx.sm_count ? p.total_work : ctx.sm_count;
+  fa_fwd_kernel<D, kCausal><<<grid, kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, p);
+  PTXB200_CUDA_TRY(cudaGetLastError());
+  return PTXB200_OK;
+}
+
+}  // namespace
+
+int launch_fa_fwd(const DeviceCtx& ctx, void* O, const void* Q, const void* K, const void* V,
+                  int B, int H, int S, int D, float sm_scale, int causal, unsigned flags,
+                  void* dbg, uint32_t* status, cudaStream_t stream) {
+  const uint64_t rows = (uint64_t)B * H * S;
+  CUtensorMap tq, tk, tv;
+  int rc;
+  if ((rc = encode_tmap_bf16_2d(&tq, Q, rows, D, (uint64_t)D * 2, 128, 64)) != PTXB200_OK) return rc;
+  if ((rc = encode_tmap_bf16_2d(&tk, K, rows, D, (uint64_t)D * 2, 128, 64)) != PTXB200_OK) return rc;
+  if ((rc = encode_tmap_bf16_2d(&tv, V, rows, D, (uint64_t)D * 2, 128, 64)) != PTXB200_OK) return rc;
+  FaParams p;
+  p.o = reinterpret_cast<__nv_bfloat16*>(O);
+  p.seqlen = S;
+  p.num_mblocks = S / 256;
+  p.bh = B * H;
+  p.total_work = p.num_mblocks * p.bh;
+  p.scale_log2 = sm_scale * 1.4426950408889634f;
+  p.rescale_threshold = (flags & PTXB200_FA_NO_LAZY_RESCALE) ? 0.0f : 8.0f;
+  p.status = status;
+  p.dbg = reinterpret_cast<uint32_t*>(dbg);
+  if (D == 128) {
+    return causal ? launch_variant<128, true>(ctx, tq, tk, tv, p, stream)
+                  : launch_variant<128, false>(ctx, tq, tk, tv, p, stream);
+  }
+  return causal ? launch_variant<64, true>(ctx, tq, tk, tv, p, stream)
+                : launch_variant<64, false>(ctx, tq, tk, tv, p, stream);
+}
+
+}  // namespace ptxb200

@@ -1,0 +1,68 @@
+// Host-side plumbing shared by the entry points: per-device context (SM count,
+// capability, status/workspace words), tensor-map encoding through the driver
+// entry point, and error bookkeeping.
+//
+// Reference counterpart: ext/CUDACoreExt.jl:44-71,114-140 (cuTensorMapEncodeTiled
+// call and descriptor upload). Here the 128-byte tensor map is passed to the
+// kernel by value as a __grid_constant__ parameter, so there is no upload step
+// and no per-call device allocation.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/ptxb200.h"
+
+namespace ptxb200 {
+
+// Words of the per-device workspace (uint32 each).
+enum : int {
+  kWsStatus = 0,       // first-blame status word written by bounded waits
+  kWsWords = 64,
+};
+
+struct DeviceCtx {
+  int device = -1;
+  int sm_count = 0;
+  int cc_major = 0;
+  int cc_minor = 0;
+  uint32_t* workspace = nullptr;  // kWsWords uint32 on the device, zero-initialised once
+};
+
+// Context of the device current in the calling thread (created on first use).
+// Returns PTXB200_OK or a negative code.
+int current_ctx(DeviceCtx** out);
+
+// Every cached context (for shutdown).
+int release_all_ctx();
+
+// Record / fetch the calling thread's last CUDA error text.
+void set_cuda_error(const char* what, cudaError_t e);
+void set_error_text(const char* what);
+const char* get_cuda_error();
+
+// 2-D row-major bf16 tensor map: `rows` x `cols` elements, row pitch
+// `row_pitch_bytes`, box `box_rows` x `box_cols`, 128-byte swizzle.
+// (ext/CUDACoreExt.jl:114-131: dims innermost-first = (cols, rows).)
+int encode_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols,
+                        uint64_t row_pitch_bytes, uint32_t box_rows, uint32_t box_cols);
+
+#define PTXB200_CUDA_TRY(expr)                         \
+  do {                                                 \
+    cudaError_t _e = (expr);                           \
+    if (_e != cudaSuccess) {                           \
+      ::ptxb200::set_cuda_error(#expr, _e);            \
+      return PTXB200_E_CUDA;                           \
+    }                                                  \
+  } while (0)
+
+// Kernel launchers (one per .cu file).
+int launch_gemm(const DeviceCtx& ctx, void* C, const void* A, const void* Bt, int M, int N, int K,
+                int ldc, unsigned flags, cudaStream_t stream);
+int launch_fa_fwd(const DeviceCtx& ctx, void* O, const void* Q, const void* K, const void* V,
+                  int B, int H, int S, int D, float sm_scale, int causal, unsigned flags,
+                  void* dbg, uint32_t* status, cudaStream_t stream);
+int launch_selftest(const DeviceCtx& ctx, int which, void* out_s, void* out_o, const void* q,
+                    const void* k, const void* v, const void* p, cudaStream_t stream);
+
+}  // namespace ptxb200

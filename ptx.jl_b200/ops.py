@@ -1,0 +1,112 @@
+"""Tensor-level calls into libptxb200.so.
+
+torch supplies device memory and streams only; each function validates what it
+can on the host, then hands raw device pointers to the C ABI
+(include/ptxb200.h). Nothing here computes: without the compiled library and a
+compute-capability-10.x GPU these functions raise.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import Optional
+
+import torch
+
+from . import native
+
+
+def _ptr(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream(stream: Optional[torch.cuda.Stream]) -> ctypes.c_void_p:
+    s = torch.cuda.current_stream() if stream is None else stream
+    return ctypes.c_void_p(s.cuda_stream)
+
+
+def _require_cuda(*tensors: torch.Tensor) -> None:
+    for t in tensors:
+        if not t.is_cuda:
+            raise ValueError("ptxb200 ops take CUDA tensors (the library has no CPU path)")
+        if not t.is_contiguous():
+            raise ValueError("ptxb200 ops take contiguous tensors")
+
+
+def fa_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: bool = False,
+           sm_scale: Optional[float] = None, out: Optional[torch.Tensor] = None,
+           flags: int = 0, dbg: Optional[torch.Tensor] = None,
+           stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
+    """O = softmax(Q K^T * sm_scale [+causal]) V for [B,H,S,D] bf16 tensors.
+
+    Same operand layout as the reference's fab_setup (bench/flash_attention.jl:41-85):
+    [B,H,S,D] row-major == a (B*H*S, D) matrix with D contiguous.
+    """
+    _require_cuda(q, k, v)
+    if q.dtype != torch.bfloat16 or k.dtype != torch.bfloat16 or v.dtype != torch.bfloat16:
+        raise ValueError("fa_fwd takes bf16 tensors")
+    if q.dim() != 4 or q.shape != k.shape or q.shape != v.shape:
+        raise ValueError("fa_fwd takes three [B,H,S,D] tensors of equal shape")
+    B, H, S, D = q.shape
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(D)
+    if out is None:
+        out = torch.empty_like(q)
+    else:
+        _require_cuda(out)
+        if out.shape != q.shape or out.dtype != torch.bfloat16:
+            raise ValueError("out must match q")
+    rc = native.lib().fa_fwd_bf16(_ptr(out), _ptr(q), _ptr(k), _ptr(v), B, H, S, D,
+                                  ctypes.c_float(sm_scale), int(bool(causal)), flags, _ptr(dbg),
+                                  _stream(stream))
+    native.check(rc)
+    return out
+
+
+def gemm(a: torch.Tensor, bt: torch.Tensor, *, out: Optional[torch.Tensor] = None,
+         f32_out: bool = False, stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
+    """C[M,N] = A[M,K] @ B[K,N] with B passed column-major, i.e. as Bt = B^T [N,K].
+
+    Operand packing of the reference's _run_ghb
+    (test/gpu/blackwell/gemm_highperf_blackwell.jl:236-252).
+    """
+    _require_cuda(a, bt)
+    if a.dtype != torch.bfloat16 or bt.dtype != torch.bfloat16:
+        raise ValueError("gemm takes bf16 operands")
+    if a.dim() != 2 or bt.dim() != 2 or a.shape[1] != bt.shape[1]:
+        raise ValueError("gemm takes A[M,K] and Bt[N,K]")
+    M, K = a.shape
+    N = bt.shape[0]
+    if out is None:
+        out = torch.empty((M, N), device=a.device, dtype=torch.float32 if f32_out else torch.bfloat16)
+    else:
+        _require_cuda(out)
+    ldc = out.stride(0)
+    rc = native.lib().gemm_bf16(_ptr(out), _ptr(a), _ptr(bt), M, N, K, ldc,
+                                native.GEMM_F32_OUT if f32_out else 0, _stream(stream))
+    native.check(rc)
+    return out
+
+
+def selftest(which: int, q=None, k=None, v=None, p=None):
+    """Run bring-up probe `which` (see ptxb200_selftest). Returns (out_s, out_o)."""
+    dev = torch.device("cuda", torch.cuda.current_device())
+    if which == 0:
+        out_s = torch.zeros(128 * 128, dtype=torch.int32, device=dev)
+        rc = native.lib().ptxb200_selftest(0, _ptr(out_s), None, None, None, None, None, _stream(None))
+        native.check(rc)
+        return out_s.view(128, 128), None
+    D = 128 if which == 1 else 64
+    _require_cuda(q, k, v, p)
+    out_s = torch.zeros((128, 128), dtype=torch.float32, device=dev)
+    out_o = torch.zeros((128, D), dtype=torch.float32, device=dev)
+    rc = native.lib().ptxb200_selftest(which, _ptr(out_s), _ptr(out_o), _ptr(q), _ptr(k), _ptr(v),
+                                       _ptr(p), _stream(None))
+    native.check(rc)
+    return out_s, out_o
+
+
+def sync_status(stream: Optional[torch.cuda.Stream] = None) -> int:
+    """Synchronise and return (and clear) the device status word; 0 = healthy."""
+    s = torch.cuda.current_stream() if stream is None else stream
+    return native.sync_status(s.cuda_stream)

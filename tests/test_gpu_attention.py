@@ -1,0 +1,104 @@
+"""fa_fwd_bf16 parity against the CPU oracle, through the C ABI.
+
+The small shapes and input scales are the reference's own runtime cases
+(test/gpu/blackwell/flash_attention.jl:202-221: (1,1,256), (1,2,512), (2,4,1024)
+with input scale 0.5 for Q,K and 1 for V, plus the rescale-heavy scale 2.0 case;
+causal and D = 64 cases follow test/gpu/ampere/flash_attention.jl:350-360).
+Tolerance: max abs <= 2e-2 and mean abs <= 2e-3 against the fp32 oracle.
+"""
+import numpy as np
+import pytest
+import torch
+
+from util import ATTN_MAX_ABS, ATTN_MEAN_ABS, attn_errors, bits, seeded_qkv
+
+pytestmark = pytest.mark.gpu
+
+
+def _run(pkg, gpu, oracle_mod, B, H, S, D, causal, sigma_qk, sigma_v=1.0, flags=0, seed=None):
+    seed = seed if seed is not None else B * 7919 + H * 131 + S
+    q, k, v = seeded_qkv(B, H, S, D, seed, sigma_qk, sigma_v)
+    o = pkg.ops.fa_fwd(q.to(gpu), k.to(gpu), v.to(gpu), causal=causal, flags=flags)
+    status = pkg.ops.sync_status()
+    assert status == 0, pkg.native.strerror(status)
+    ref = oracle_mod.attention_ref_c(bits(q).reshape(B * H, S, D), bits(k).reshape(B * H, S, D),
+                                     bits(v).reshape(B * H, S, D), 1.0 / D ** 0.5, causal)
+    return attn_errors(o, ref)
+
+
+@pytest.mark.parametrize("B,H,S", [(1, 1, 256), (1, 2, 512), (2, 4, 1024)])
+@pytest.mark.parametrize("D", [128, 64])
+@pytest.mark.parametrize("causal", [False, True])
+def test_reference_shapes(pkg, gpu, oracle_mod, B, H, S, D, causal):
+    mx, mean = _run(pkg, gpu, oracle_mod, B, H, S, D, causal, sigma_qk=0.5)
+    assert mx <= ATTN_MAX_ABS and mean <= ATTN_MEAN_ABS, (mx, mean)
+
+
+@pytest.mark.parametrize("D", [128, 64])
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("flags", [0, 1])
+def test_rescale_heavy(pkg, gpu, oracle_mod, D, causal, flags):
+    """Input scale 2.0 makes row maxima move by far more than 2^8 between tiles, so
+    the O-rescale path runs (flash_attention.jl:210-221); flags=1 rescales on every
+    increase of the maximum."""
+    mx, mean = _run(pkg, gpu, oracle_mod, 1, 2, 512, D, causal, sigma_qk=2.0, flags=flags)
+    assert mx <= 5e-2 and mean <= 4e-3, (mx, mean)   # the reference's gate for this input
+
+
+@pytest.mark.parametrize("D,causal", [(128, False), (128, True), (64, False), (64, True)])
+def test_many_items_per_cta(pkg, gpu, oracle_mod, D, causal):
+    """More work items than SMs: every role walks its persistent loop several times
+    (phase bookkeeping across items), including the causal longest-first order."""
+    mx, mean = _run(pkg, gpu, oracle_mod, 2, 40, 768, D, causal, sigma_qk=1.0)
+    assert mx <= ATTN_MAX_ABS and mean <= ATTN_MEAN_ABS, (mx, mean)
+
+
+def test_baseline_config_1_shape(pkg, gpu, oracle_mod):
+    """B=1 H=4 S=256 D=64 non-causal, N(0,1) inputs: the CPU-runnable baseline case."""
+    mx, mean = _run(pkg, gpu, oracle_mod, 1, 4, 256, 64, False, sigma_qk=1.0, seed=20260001)
+    assert mx <= ATTN_MAX_ABS and mean <= ATTN_MEAN_ABS, (mx, mean)
+
+
+def test_large_logits_do_not_overflow(pkg, gpu, oracle_mod):
+    """Scores of several hundred: a softmax that exponentiated the first tile
+    without subtracting its maximum would overflow; this one must not."""
+    mx, mean = _run(pkg, gpu, oracle_mod, 1, 1, 512, 128, False, sigma_qk=6.0)
+    assert np.isfinite(mx) and mx <= 5e-2, (mx, mean)
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_full_size_properties(pkg, gpu, causal):
+    """Size-independent properties at a BASELINE-sized slice (S = 4096, D = 128):
+    with V = all ones every output is exactly 1 (rows of P sum to 1); with one-hot
+    structure in V the output rows are convex combinations, so 0 <= O <= 1; and a
+    second launch on the same inputs is bit-identical (no race)."""
+    B, H, S, D = 1, 8, 4096, 128
+    q, k, _ = seeded_qkv(B, H, S, D, 99, 1.0)
+    q, k = q.to(gpu), k.to(gpu)
+    ones = torch.ones(B, H, S, D, dtype=torch.bfloat16, device=gpu)
+    o = pkg.ops.fa_fwd(q, k, ones, causal=causal)
+    assert pkg.ops.sync_status() == 0
+    assert torch.allclose(o.float(), torch.ones_like(o, dtype=torch.float32), atol=2 ** -7)
+    v = (torch.rand(B, H, S, D, device=gpu) < 0.5).to(torch.bfloat16)
+    o1 = pkg.ops.fa_fwd(q, k, v, causal=causal)
+    o2 = pkg.ops.fa_fwd(q, k, v, causal=causal)
+    assert pkg.ops.sync_status() == 0
+    assert torch.equal(o1, o2)
+    assert float(o1.float().min()) >= 0.0 and float(o1.float().max()) <= 1.0 + 2 ** -7
+    if causal:
+        # the first query row attends to key 0 only
+        assert torch.equal(o1[:, :, 0, :], v[:, :, 0, :])
+
+
+def test_rejects_bad_arguments(pkg, gpu):
+    L = pkg.native.lib()
+    t = torch.zeros(1, 1, 256, 128, dtype=torch.bfloat16, device=gpu)
+    P = t.data_ptr()
+    import ctypes
+    sc = ctypes.c_float(0.1)
+    assert L.fa_fwd_bf16(P, P, P, P, 1, 1, 200, 128, sc, 0, 0, None, None) == pkg.native.E_SHAPE
+    assert L.fa_fwd_bf16(P, P, P, P, 1, 1, 256, 96, sc, 0, 0, None, None) == pkg.native.E_SHAPE
+    assert L.fa_fwd_bf16(None, P, P, P, 1, 1, 256, 128, sc, 0, 0, None, None) == pkg.native.E_INVALID
+    assert L.fa_fwd_bf16(P, P + 2, P, P, 1, 1, 256, 128, sc, 0, 0, None, None) == pkg.native.E_ALIGN
+    assert L.fa_fwd_bf16(P, P, P, P, 1, 1, 256, 128, sc, 2, 0, None, None) == pkg.native.E_INVALID
+    assert L.fa_fwd_bf16(P, P, P, P, 1, 1, 256, 128, sc, 0, 0x80, None, None) == pkg.native.E_INVALID

@@ -1,0 +1,47 @@
+"""Bring-up probes with known answers, through the C ABI (ptxb200_selftest).
+
+Restates the reference's single-instruction runtime tests: TMEM round-trip
+identity (test/gpu/blackwell/tcgen05_roundtrip.jl:78-88) and single-MMA known
+answers (tcgen05_mma_probe.jl:122-129: ones x ones over K=16 -> 16.0), plus the
+non-uniform operand forms the attention kernel depends on.
+"""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def test_tmem_roundtrip(pkg, gpu):
+    out_s, _ = pkg.ops.selftest(0)
+    assert pkg.ops.sync_status() == 0
+    got = out_s.cpu().numpy().view(np.uint32)
+    r = np.arange(128, dtype=np.uint32)[:, None]
+    c = np.arange(128, dtype=np.uint32)[None, :]
+    assert np.array_equal(got, ((r << 16) | c) ^ np.uint32(0x5A5A0000))
+
+
+@pytest.mark.parametrize("which,D", [(1, 128), (2, 64)])
+def test_tile_ones(pkg, gpu, which, D):
+    """All-ones operands: S = D, O = 128 exactly (the reference's 16.0 probe, scaled)."""
+    one = lambda *s: torch.ones(*s, dtype=torch.bfloat16, device=gpu)
+    out_s, out_o = pkg.ops.selftest(which, one(128, D), one(128, D), one(128, D), one(128, 128))
+    assert pkg.ops.sync_status() == 0
+    assert torch.all(out_s == float(D))
+    assert torch.all(out_o == 128.0)
+
+
+@pytest.mark.parametrize("which,D", [(1, 128), (2, 64)])
+def test_tile_random(pkg, gpu, oracle_mod, which, D):
+    """Non-uniform data: exercises the swizzled K-major descriptors, the MN-major V
+    descriptor and P read from tensor memory. Products of bf16 values accumulate
+    exactly enough in fp32 for a tight tolerance."""
+    g = torch.Generator().manual_seed(77 + D)
+    q, k, v = (torch.randn(128, D, generator=g).to(torch.bfloat16) for _ in range(3))
+    p = torch.rand(128, 128, generator=g).to(torch.bfloat16)
+    out_s, out_o = pkg.ops.selftest(which, q.to(gpu), k.to(gpu), v.to(gpu), p.to(gpu))
+    assert pkg.ops.sync_status() == 0
+    s_ref = q.float().numpy() @ k.float().numpy().T
+    o_ref = p.float().numpy() @ v.float().numpy()
+    np.testing.assert_allclose(out_s.cpu().numpy(), s_ref, rtol=1e-4, atol=1e-3)
+    np.testing.assert_allclose(out_o.cpu().numpy(), o_ref, rtol=1e-4, atol=1e-3)
