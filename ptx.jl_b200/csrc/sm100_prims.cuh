@@ -67,6 +67,18 @@ static_assert(make_idesc_bf16_f32(128, 128, false, true) ==
                   ((1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | (16u << 17) | (8u << 24)),
               "idesc formula, MN-major B");
 
+// Descriptors travel as (lo, hi) 32-bit halves: every per-step variation (the
+// start address) lives in `lo`, `hi` is a constant of the layout, so stepping
+// through a tile costs one 32-bit add per operand.
+__host__ __device__ constexpr uint32_t sdesc_lo(uint32_t smem_addr, uint32_t leading_bytes) {
+  return (uint32_t)(make_sdesc(smem_addr, leading_bytes, 0, 0) & 0xFFFFFFFFull);
+}
+__host__ __device__ constexpr uint32_t sdesc_hi(uint32_t stride_bytes, uint32_t layout) {
+  return (uint32_t)(make_sdesc(0, 0, stride_bytes, layout) >> 32);
+}
+static_assert((((uint64_t)sdesc_hi(1024, kLayoutB128) << 32) | sdesc_lo(0, 16)) ==
+                  0x4000404000010000ull, "split descriptor equals the packed one");
+
 // TMEM address = (lane << 16) + column (src/lib/tcgen05_layout.jl:36).
 __host__ __device__ constexpr uint32_t tmem_addr(uint32_t base, uint32_t lane, uint32_t col) {
   return base + (lane << 16) + col;
@@ -220,18 +232,6 @@ __device__ __forceinline__ void tc_commit(uint32_t bar) {
                    bar)
                : "memory");
 }
-
-// Descriptors travel as (lo, hi) 32-bit halves: every per-step variation (the
-// start address) lives in `lo`, `hi` is a constant of the layout, so stepping
-// through a tile costs one 32-bit add per operand.
-__host__ __device__ constexpr uint32_t sdesc_lo(uint32_t smem_addr, uint32_t leading_bytes) {
-  return (uint32_t)(make_sdesc(smem_addr, leading_bytes, 0, 0) & 0xFFFFFFFFull);
-}
-__host__ __device__ constexpr uint32_t sdesc_hi(uint32_t stride_bytes, uint32_t layout) {
-  return (uint32_t)(make_sdesc(0, 0, stride_bytes, layout) >> 32);
-}
-static_assert((((uint64_t)sdesc_hi(1024, kLayoutB128) << 32) | sdesc_lo(0, 16)) ==
-                  0x4000404000010000ull, "split descriptor equals the packed one");
 
 // D[tmem] (+)= A[smem desc] * B[smem desc]; one thread issues.
 __device__ __forceinline__ void tc_mma_ss(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi,
