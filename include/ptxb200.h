@@ -102,6 +102,44 @@ int fa_fwd_bf16(void* O, const void* Q, const void* K, const void* V, int B, int
                 float sm_scale, int causal, unsigned flags, void* dbg, void* stream);
 
 /*
+ * fa_fwd_bf16 without any allocation. (No counterpart in the reference: its
+ * launch closure allocates nothing per call either, but its set-up uploads three
+ * descriptor blobs into freshly allocated device memory.)
+ *
+ * Who needs it: a caller that must not cause a device allocation at the point
+ * where it launches attention -- a serving loop that carved up all device memory
+ * beforehand and treats any later cudaMalloc as an error (or would simply fail,
+ * the device being full), a latency-critical section where the implicit
+ * synchronisation of cudaMalloc is unacceptable, or a host runtime with its own
+ * device memory pool (a Julia or Python session) that wants every byte on the GPU
+ * to come from that pool. fa_fwd_bf16 is unsuitable there because its first call
+ * on a device cudaMalloc's the library's small workspace.
+ *
+ * How: the kernel's scratch (the status word of its bounded waits plus one
+ * "this CTA timed out" flag per CTA) lives in a 1 KiB array that is part of the
+ * loaded library image, so every GPU that loads libptxb200.so holds that 1 KiB
+ * until the process exits. This function never calls cudaMalloc, cudaFree or any
+ * allocating routine. Arguments, layout, shape contract and results are those of
+ * fa_fwd_bf16 (same kernel code); there is no dbg argument.
+ *
+ * Limits and rules
+ *   - Capacity: at most 240 CTAs (one per SM) and device ordinals 0..63; beyond
+ *     that the call returns PTXB200_E_CAPACITY and launches nothing.
+ *   - The first call on each device looks up the array's device address and sets
+ *     kernel attributes. Make that first call outside any stream capture.
+ *   - All calls on one device share the one array. The function clears what must
+ *     start at zero on `stream` before each launch, so calls that follow each
+ *     other on a stream are fine; calls that can overlap on the GPU (different
+ *     streams, or different host threads launching on the same device) race on
+ *     the status word and flags. The attention results themselves do not depend
+ *     on the scratch contents unless a wait runs out.
+ *   - ptxb200_sync_status() reports on fa_fwd_bf16/gemm_bf16 launches only; it
+ *     does not read this array (it would allocate the workspace).
+ */
+int fa_fwd_bf16_noalloc(void* O, const void* Q, const void* K, const void* V, int B, int H, int S,
+                        int D, float sm_scale, int causal, unsigned flags, void* stream);
+
+/*
  * Synchronise `stream`, then return and clear the current device's status word:
  * 0 if every kernel enqueued through this library since the last call ran to
  * completion normally, a positive code if a bounded device-side wait ran out

@@ -33,6 +33,8 @@
 // (softmax excluded; the reference's convention, bench/flash_attention.jl:107-108).
 #include <math.h>
 
+#include <mutex>
+
 #include "attn_tiles.cuh"
 #include "host_common.h"
 
@@ -89,6 +91,7 @@ struct FaParams {
   float rescale_threshold;  // in log2 units of the scaled scores
   uint32_t* status;
   uint32_t* dbg;
+  uint32_t* cta_flags;  // only read by the kCtaFlags variant: one word per CTA
 };
 
 // Work item -> (m_block, batch*head). Non-causal: m_block fastest, so CTAs that
@@ -115,7 +118,10 @@ __device__ __forceinline__ void tile_counts(const FaParams& p, int mb, int& nt0,
   }
 }
 
-template <int D, bool kCausal>
+// kCtaFlags: additionally mark, in p.cta_flags[blockIdx.x], every CTA in which a
+// bounded wait ran out (used by the entry point that keeps its scratch in a static
+// device array).
+template <int D, bool kCausal, bool kCtaFlags = false>
 __global__ void __launch_bounds__(kThreads, 1)
 fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
               const __grid_constant__ CUtensorMap tmap_v, const FaParams p) {
@@ -448,6 +454,9 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
     tc_fence_after();
     tmem_dealloc(tmem, 512);
   }
+  if (kCtaFlags) {
+    if (tid == 0 && *abort_flag != 0) p.cta_flags[blockIdx.x] = 1u;
+  }
 }
 
 template <int D, bool kCausal>
@@ -488,6 +497,7 @@ int launch_fa_fwd(const DeviceCtx& ctx, void* O, const void* Q, const void* K, c
   p.rescale_threshold = (flags & PTXB200_FA_NO_LAZY_RESCALE) ? 0.0f : 8.0f;
   p.status = status;
   p.dbg = reinterpret_cast<uint32_t*>(dbg);
+  p.cta_flags = nullptr;
   if (D == 128) {
     return causal ? launch_variant<128, true>(ctx, tq, tk, tv, p, stream)
                   : launch_variant<128, false>(ctx, tq, tk, tv, p, stream);
@@ -497,3 +507,151 @@ int launch_fa_fwd(const DeviceCtx& ctx, void* O, const void* Q, const void* K, c
 }
 
 }  // namespace ptxb200
+
+// ===========================================================================
+// fa_fwd_bf16_noalloc: the same kernel with its scratch in a static device array
+// ===========================================================================
+//
+// fa_fwd_bf16 keeps its scratch -- the status word its bounded waits report to --
+// in a per-device workspace that the library cudaMalloc's on first use. Some
+// callers must not trigger an allocation: a serving loop whose device memory was
+// carved up front (a later cudaMalloc is an error there, or fails on a full
+// device), a latency-critical section that cannot take cudaMalloc's implicit
+// synchronisation, a host runtime (such as a Julia session with its own memory
+// pool) that wants to own every byte on the device. For them this entry point keeps the scratch in
+// the array below. The array is part of the loaded module: every GPU that loads
+// this library holds its kNoAllocScratchBytes until the process exits.
+//
+// Layout (uint32 words): [0] status word (first-blame code of a wait that ran
+// out, as in fa_fwd_bf16), [1..15] reserved, [16 .. 16 + kNoAllocMaxCtas) one flag
+// per CTA, set when a wait of that CTA ran out.
+//
+// The host-side name of a __device__ array is not a device address; the address
+// the kernel gets comes from cudaGetSymbolAddress, asked once per device with
+// that device current.
+namespace ptxb200 {
+namespace {
+
+constexpr int kNoAllocMaxCtas = 240;                                 // one CTA per SM
+constexpr int kNoAllocFlagBase = 16;
+constexpr int kNoAllocScratchWords = kNoAllocFlagBase + kNoAllocMaxCtas;   // 256 words
+constexpr int kNoAllocScratchBytes = kNoAllocScratchWords * 4;             // 1 KiB
+static __device__ __align__(256) uint32_t g_noalloc_scratch[kNoAllocScratchWords];
+
+struct NoAllocDevice {
+  bool ready = false;
+  uint32_t* scratch = nullptr;   // device address of g_noalloc_scratch on this device
+  int sm_count = 0;
+};
+constexpr int kNoAllocMaxDevices = 64;
+NoAllocDevice g_noalloc_dev[kNoAllocMaxDevices];
+std::mutex g_noalloc_mu;
+
+static_assert(kNoAllocScratchBytes == 1024, "documented size of the static scratch array");
+
+template <int D, bool kCausal>
+int noalloc_prepare() {   // opt in to the large dynamic shared memory of one variant
+  PTXB200_CUDA_TRY(cudaFuncSetAttribute(fa_fwd_kernel<D, kCausal, true>,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        FaCfg<D>::kSmemBytes));
+  return PTXB200_OK;
+}
+
+template <int D, bool kCausal>
+int noalloc_launch(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                   const FaParams& p, int grid, cudaStream_t stream) {
+  using C = FaCfg<D>;
+  fa_fwd_kernel<D, kCausal, true><<<grid, kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, p);
+  PTXB200_CUDA_TRY(cudaGetLastError());
+  return PTXB200_OK;
+}
+
+}  // namespace
+}  // namespace ptxb200
+
+extern "C" int fa_fwd_bf16_noalloc(void* O, const void* Q, const void* K, const void* V, int B,
+                                   int H, int S, int D, float sm_scale, int causal,
+                                   unsigned flags, void* stream_v) {
+  using namespace ptxb200;
+  auto aligned16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+  if (O == nullptr || Q == nullptr || K == nullptr || V == nullptr) return PTXB200_E_INVALID;
+  if (B <= 0 || H <= 0 || S <= 0 || D <= 0) return PTXB200_E_INVALID;
+  if (causal != 0 && causal != 1) return PTXB200_E_INVALID;
+  if (flags & ~PTXB200_FA_NO_LAZY_RESCALE) return PTXB200_E_INVALID;
+  if (!(sm_scale > 0.0f) || !(sm_scale < 1e30f)) return PTXB200_E_INVALID;
+  if ((D != 64 && D != 128) || S % 256 != 0) return PTXB200_E_SHAPE;
+  if ((long long)B * H * S >= (1ll << 31)) return PTXB200_E_SHAPE;
+  if (!aligned16(O) || !aligned16(Q) || !aligned16(K) || !aligned16(V)) return PTXB200_E_ALIGN;
+  cudaStream_t stream = (cudaStream_t)stream_v;
+
+  int dev = -1;
+  PTXB200_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kNoAllocMaxDevices) {
+    set_error_text("fa_fwd_bf16_noalloc: device ordinal beyond the 64 this entry point tracks");
+    return PTXB200_E_CAPACITY;
+  }
+  NoAllocDevice nd;
+  {
+    std::lock_guard<std::mutex> lock(g_noalloc_mu);
+    NoAllocDevice& slot = g_noalloc_dev[dev];
+    if (!slot.ready) {
+      // one-time set-up for this device (it is the current one): capability, SM
+      // count and the DEVICE address of the static scratch array. Because the first
+      // call on a device does this, that call should come before any stream capture.
+      int cc_major = 0;
+      PTXB200_CUDA_TRY(cudaDeviceGetAttribute(&cc_major, cudaDevAttrComputeCapabilityMajor, dev));
+      if (cc_major != 10) {
+        set_error_text("current device is not compute capability 10.x (sm_100a code only)");
+        return PTXB200_E_DEVICE;
+      }
+      PTXB200_CUDA_TRY(cudaDeviceGetAttribute(&slot.sm_count, cudaDevAttrMultiProcessorCount, dev));
+      void* ptr = nullptr;
+      PTXB200_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
+      slot.scratch = reinterpret_cast<uint32_t*>(ptr);
+      int rc;
+      if ((rc = noalloc_prepare<128, false>()) != PTXB200_OK) return rc;
+      if ((rc = noalloc_prepare<128, true>()) != PTXB200_OK) return rc;
+      if ((rc = noalloc_prepare<64, false>()) != PTXB200_OK) return rc;
+      if ((rc = noalloc_prepare<64, true>()) != PTXB200_OK) return rc;
+      slot.ready = true;
+    }
+    nd = slot;
+  }
+
+  FaParams p;
+  p.o = reinterpret_cast<__nv_bfloat16*>(O);
+  p.seqlen = S;
+  p.num_mblocks = S / 256;
+  p.bh = B * H;
+  p.total_work = p.num_mblocks * p.bh;
+  p.scale_log2 = sm_scale * 1.4426950408889634f;
+  p.rescale_threshold = (flags & PTXB200_FA_NO_LAZY_RESCALE) ? 0.0f : 8.0f;
+  p.status = nd.scratch;
+  p.dbg = nullptr;
+  p.cta_flags = nd.scratch + kNoAllocFlagBase;
+  const int grid = p.total_work < nd.sm_count ? p.total_work : nd.sm_count;
+  if (grid > kNoAllocMaxCtas) {
+    set_error_text("fa_fwd_bf16_noalloc: launch needs more CTAs than the 240 flag slots of the "
+                   "static scratch array");
+    return PTXB200_E_CAPACITY;
+  }
+
+  const uint64_t rows = (uint64_t)B * H * S;
+  CUtensorMap tq, tk, tv;
+  int rc;
+  if ((rc = encode_tmap_bf16_2d(&tq, Q, rows, D, (uint64_t)D * 2, 128, 64)) != PTXB200_OK) return rc;
+  if ((rc = encode_tmap_bf16_2d(&tk, K, rows, D, (uint64_t)D * 2, 128, 64)) != PTXB200_OK) return rc;
+  if ((rc = encode_tmap_bf16_2d(&tv, V, rows, D, (uint64_t)D * 2, 128, 64)) != PTXB200_OK) return rc;
+
+  // The array keeps what the previous call left: the status word and the flags of
+  // the CTAs this launch uses must start at zero.
+  PTXB200_CUDA_TRY(cudaMemsetAsync(nd.scratch, 0, (size_t)(kNoAllocFlagBase + grid) * 4, stream));
+
+  if (D == 128) {
+    return causal ? noalloc_launch<128, true>(tq, tk, tv, p, grid, stream)
+                  : noalloc_launch<128, false>(tq, tk, tv, p, grid, stream);
+  }
+  return causal ? noalloc_launch<64, true>(tq, tk, tv, p, grid, stream)
+                : noalloc_launch<64, false>(tq, tk, tv, p, grid, stream);
+}
+
