@@ -48,11 +48,39 @@ constexpr int kRegsOther = 72;
 static_assert(256 * kRegsSoftmax + 128 * kRegsCorrection + 128 * kRegsOther <= 65536,
               "register re-split must fit the register file");
 
+// Which of the 16 element pairs of every 32-column chunk take the FMA-pipe
+// polynomial exp2 instead of the MUFU ex2 (bit i = pair i). The MUFU pipe
+// (16 ex2/clk/SM) needs as many cycles per tile as the tensor pipe at D = 128 and
+// twice as many at D = 64; moving a fraction of the exponentials to the FMA pipe
+// takes it off the critical path.
+#ifndef PTXB200_FA_EMU_MASK
+#define PTXB200_FA_EMU_MASK 0x0000u
+#endif
+constexpr uint32_t kEmuMask = PTXB200_FA_EMU_MASK;
+#ifndef PTXB200_FA_BATCH
+#define PTXB200_FA_BATCH 8
+#endif
+constexpr int kBatch = PTXB200_FA_BATCH;   // element pairs per exp batch
+
 enum : uint32_t {
   kSiteLoadQFree = 5, kSiteLoadKvFree = 6, kSiteMmaQFull = 7, kSiteMmaKvFull = 8,
   kSiteMmaPFull = 9, kSiteMmaOReady = 10, kSiteSoftmaxSFull = 11, kSiteCorrAlpha = 12,
   kSiteCorrLReady = 13, kSiteCorrODone = 14
 };
+
+// Timestamp hooks for offline latency studies; compiled out of the product build.
+#ifdef PTXB200_FA_TIMING
+#define FA_TSTAMP(cond, rec, tile, ev)                                            \
+  do {                                                                            \
+    if ((cond) && (tile) < 16 && p.dbg != nullptr) {                              \
+      long long t_;                                                               \
+      asm volatile("mov.u64 %0, %%clock64;" : "=l"(t_));                          \
+      p.dbg[16 + (((rec) * 16 + (tile)) * 8 + (ev))] = (uint32_t)t_;              \
+    }                                                                             \
+  } while (0)
+#else
+#define FA_TSTAMP(cond, rec, tile, ev) do {} while (0)
+#endif
 
 template <int D>
 struct FaCfg {
@@ -68,8 +96,8 @@ struct FaCfg {
   static constexpr int kBarKvFull = 3;                 // [kSlots] TMA tx
   static constexpr int kBarKvFree = kBarKvFull + kSlots;   // [kSlots] tcgen05.commit
   static constexpr int kBarSFull = kBarKvFree + kSlots;    // [2] tcgen05.commit
-  static constexpr int kBarPFull = kBarSFull + 2;      // [2] 128 softmax threads
-  static constexpr int kBarAlpha = kBarPFull + 2;      // [2] 128 softmax threads
+  static constexpr int kBarPFull = kBarSFull + 2;      // [2 stages][2 halves] 128 softmax threads
+  static constexpr int kBarAlpha = kBarPFull + 4;      // [2] 128 softmax threads
   static constexpr int kBarLReady = kBarAlpha + 2;     // [2] 128 softmax threads
   static constexpr int kBarOReady = kBarLReady + 2;    // [2] 128 correction threads
   static constexpr int kBarODone = kBarOReady + 2;     // [2] tcgen05.commit
@@ -155,7 +183,8 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar(C::kBarSFull + s), 1);
-      mbar_init(bar(C::kBarPFull + s), 128);
+      mbar_init(bar(C::kBarPFull + 2 * s + 0), 128);
+      mbar_init(bar(C::kBarPFull + 2 * s + 1), 128);
       mbar_init(bar(C::kBarAlpha + s), 128);
       mbar_init(bar(C::kBarLReady + s), 128);
       mbar_init(bar(C::kBarOReady + s), 128);
@@ -227,16 +256,31 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
           const uint32_t ka = kv_smem + kslot * T::kTileBytes;
 #pragma unroll
           for (int kk = 0; kk < T::kQKAtoms; ++kk)
+#if defined(PTXB200_FA_ABLATE) && (PTXB200_FA_ABLATE == 5 || PTXB200_FA_ABLATE == 6)
+            if (kk < 0)
+#endif
             tc_mma_ss(tmem + C::kColS + stage * 128, T::kmajor_lo(qa, kk), T::kKMajorHi,
                       T::kmajor_lo(ka, kk), T::kKMajorHi, T::kIdescQK, kk != 0 ? 1u : 0u);
           tc_commit(bar(C::kBarSFull + stage));
         };
-        auto pv = [&](int stage, uint32_t vslot, bool accumulate) {   // O_stage (+)= P_stage V
+        // O_stage (+)= P_stage V, issued per 64-column half of P as the softmax
+        // publishes it: k16 steps 0-3 run while the second half is still being
+        // exponentiated (the reference's split-P idea, flash_attention_defs.jl:36-50).
+        auto pv = [&](int stage, uint32_t vslot, bool accumulate, uint32_t parity) {
           const uint32_t va = kv_smem + vslot * T::kTileBytes;
 #pragma unroll
-          for (int kk = 0; kk < T::kPVAtoms; ++kk)
-            tc_mma_ts(tmem + C::kColO + stage * D, T::p_tmem(tmem, C::kColS + stage * 128, kk),
-                      T::v_lo(va, kk), T::kVHi, T::kIdescPV, (accumulate || kk != 0) ? 1u : 0u);
+          for (int h = 0; h < 2; ++h) {
+            mbar_wait(bar(C::kBarPFull + 2 * stage + h), parity, wctx, kSiteMmaPFull);
+            if (h == 0) mbar_wait(bar(C::kBarOReady + stage), parity, wctx, kSiteMmaOReady);
+            tc_fence_after();
+#pragma unroll
+            for (int kk = 4 * h; kk < 4 * h + 4; ++kk)
+#if defined(PTXB200_FA_ABLATE) && (PTXB200_FA_ABLATE == 4 || PTXB200_FA_ABLATE == 6)
+              if (kk < 0)
+#endif
+              tc_mma_ts(tmem + C::kColO + stage * D, T::p_tmem(tmem, C::kColS + stage * 128, kk),
+                        T::v_lo(va, kk), T::kVHi, T::kIdescPV, (accumulate || kk != 0) ? 1u : 0u);
+          }
         };
         for (int w = blockIdx.x; w < p.total_work; w += gridDim.x, ++item_i) {
           int mb, bh, nt[2];
@@ -254,20 +298,22 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
           tc_commit(bar(C::kBarKvFree + k0));
           if (nt_max == 1) tc_commit(bar(C::kBarQFree));
           for (int j = 0; j < nt_max; ++j) {
+            FA_TSTAMP(w == 0, 2, j, 6);
             const uint32_t vslot = kv_wait();
             const bool has_next = (j + 1 < nt_max);
             uint32_t kslot = 0;
             if (has_next) kslot = kv_wait();
+            FA_TSTAMP(w == 0, 2, j, 7);
 #pragma unroll
             for (int s = 0; s < 2; ++s) {
               if (j < nt[s]) {
-                mbar_wait(bar(C::kBarPFull + s), cnt_pv[s] & 1u, wctx, kSiteMmaPFull);
-                mbar_wait(bar(C::kBarOReady + s), cnt_pv[s] & 1u, wctx, kSiteMmaOReady);
+                FA_TSTAMP(w == 0, 2, j, 3 * s + 0);
+                pv(s, vslot, j > 0, cnt_pv[s] & 1u);
                 ++cnt_pv[s];
-                tc_fence_after();
-                pv(s, vslot, j > 0);
+                FA_TSTAMP(w == 0, 2, j, 3 * s + 1);
                 if (j + 1 < nt[s]) qk(s, kslot);
                 else tc_commit(bar(C::kBarODone + s));
+                FA_TSTAMP(w == 0, 2, j, 3 * s + 2);
               }
             }
             tc_commit(bar(C::kBarKvFree + vslot));
@@ -302,14 +348,17 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
       float l_run = 0.0f;
 #pragma unroll 1
       for (int j = 0; j < ntiles; ++j) {
+        FA_TSTAMP(w == 0 && row == 0, stage, j, 0);
         mbar_wait(bar(C::kBarSFull + stage), cnt_s & 1u, wctx, kSiteSoftmaxSFull);
         ++cnt_s;
         tc_fence_after();
+        FA_TSTAMP(w == 0 && row == 0, stage, j, 1);
         uint32_t v[4][32];
 #pragma unroll
         for (int c = 0; c < 4; ++c) tmem_ld32(t_row + c * 32, v[c]);
 #pragma unroll
         for (int c = 0; c < 4; ++c) tc_wait_ld_bind(v[c]);
+        FA_TSTAMP(w == 0 && row == 0, stage, j, 2);
 
         if (kCausal && j == ntiles - 1) {
           // diagonal tile: key (local) column i is kept iff i <= row
@@ -345,24 +394,59 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
           l_run *= alpha;
         }
 
+        FA_TSTAMP(w == 0 && row == 0, stage, j, 3);
         const float neg = -m_run * scale_log2;
-        float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        const float2 scale2 = make_float2(scale_log2, scale_log2);
+        const float2 neg2 = make_float2(neg, neg);
+        float2 sum2[2] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)};
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t pk[16];
+          // batches of kBatch pairs: all scaled inputs, then all exponentials back to
+          // back (so the MUFU latency of one is hidden behind the issue of the next),
+          // then the sums and the bf16 packing
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const float e0 = ex2_approx(fmaf(__uint_as_float(v[c][2 * i]), scale_log2, neg));
-            const float e1 = ex2_approx(fmaf(__uint_as_float(v[c][2 * i + 1]), scale_log2, neg));
-            sum[i & 3] += e0 + e1;
-            pk[i] = pack_bf16x2(e0, e1);
+          for (int b = 0; b < 16; b += kBatch) {
+            float2 x[kBatch], e[kBatch];
+#pragma unroll
+            for (int i = 0; i < kBatch; ++i)
+              x[i] = __ffma2_rn(make_float2(__uint_as_float(v[c][2 * (b + i)]),
+                                            __uint_as_float(v[c][2 * (b + i) + 1])), scale2, neg2);
+#pragma unroll
+            for (int i = 0; i < kBatch; ++i) {
+              if ((kEmuMask >> (b + i)) & 1u) {
+                e[i] = exp2_poly2(x[i]);
+              } else {
+#if defined(PTXB200_FA_ABLATE) && PTXB200_FA_ABLATE >= 3
+                e[i] = __ffma2_rn(x[i], x[i], x[i]);
+#else
+                e[i].x = ex2_approx(x[i].x);
+                e[i].y = ex2_approx(x[i].y);
+#endif
+              }
+            }
+#pragma unroll
+            for (int i = 0; i < kBatch; ++i) {
+#if !(defined(PTXB200_FA_ABLATE) && PTXB200_FA_ABLATE == 2)
+              sum2[i & 1] = __fadd2_rn(sum2[i & 1], e[i]);
+#endif
+#if defined(PTXB200_FA_ABLATE) && PTXB200_FA_ABLATE == 1
+              pk[b + i] = __float_as_uint(e[i].x) ^ __float_as_uint(e[i].y);
+#else
+              pk[b + i] = pack_bf16x2(e[i].x, e[i].y);
+#endif
+            }
           }
           tmem_st16(t_row + c * 16, pk);
+          if (c & 1) {
+            // one 64-column half of P is in tensor memory: publish it
+            tc_wait_st();
+            tc_fence_before();
+            mbar_arrive(bar(C::kBarPFull + 2 * stage + (c >> 1)));
+            FA_TSTAMP(w == 0 && row == 0, stage, j, 4 + (c >> 1));
+          }
         }
-        tc_wait_st();
-        tc_fence_before();
-        mbar_arrive(bar(C::kBarPFull + stage));
-        l_run += (sum[0] + sum[1]) + (sum[2] + sum[3]);
+        l_run += (sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y);
       }
       stats_l[stage * 128 + row] = l_run;
       mbar_arrive(bar(C::kBarLReady + stage));

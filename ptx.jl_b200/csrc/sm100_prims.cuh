@@ -324,6 +324,32 @@ __device__ __forceinline__ float ex2_approx(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// 2^x for two values on the FMA pipe (no MUFU): x = n + f with n = floor(x),
+// 2^f by a degree-3 minimax polynomial on [0,1) (max relative error 7.5e-5, far
+// below the bf16 rounding that follows), n added into the exponent field.
+// floor comes from adding 1.5*2^23 in round-down mode, which leaves n in the low
+// mantissa bits; (bits << 23) drops the constant's bits, so one shift-add per value
+// finishes the job. Inputs below -126 are clamped (the polynomial dips just below 1
+// at f = 0, so n = -127 would borrow from the sign bit; 2^-126 is zero for every
+// purpose here).
+// Same role as the reference's fab_exp_pair_emu
+// (test/gpu/blackwell/flash_attention_defs.jl:355-387); coefficients derived here
+// by a Remez exchange on the relative error.
+__device__ __forceinline__ float2 exp2_poly2(float2 x) {
+  const float kMagic = 12582912.0f;  // 1.5 * 2^23
+  x.x = fmaxf(x.x, -126.0f);
+  x.y = fmaxf(x.y, -126.0f);
+  const float2 r = __fadd2_rd(x, make_float2(kMagic, kMagic));
+  const float2 fl = __fadd2_rn(r, make_float2(-kMagic, -kMagic));
+  const float2 f = __ffma2_rn(fl, make_float2(-1.0f, -1.0f), x);
+  float2 p = __ffma2_rn(f, make_float2(0.07802452f, 0.07802452f), make_float2(0.22606716f, 0.22606716f));
+  p = __ffma2_rn(p, f, make_float2(0.69583356f, 0.69583356f));
+  p = __ffma2_rn(p, f, make_float2(0.99992520f, 0.99992520f));
+  float2 e;
+  e.x = __uint_as_float(__float_as_uint(p.x) + (__float_as_uint(r.x) << 23));
+  e.y = __uint_as_float(__float_as_uint(p.y) + (__float_as_uint(r.y) << 23));
+  return e;
+}
 __device__ __forceinline__ float rcp_approx(float x) {
   float y;
   asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));

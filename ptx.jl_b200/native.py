@@ -12,7 +12,8 @@ import re
 from typing import List, Optional
 
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(PKG_DIR, "libptxb200.so")
+# PTXB200_LIB_PATH overrides the in-tree library (e.g. an instrumented build)
+LIB_PATH = os.environ.get("PTXB200_LIB_PATH") or os.path.join(PKG_DIR, "libptxb200.so")
 HEADER_PATH = os.path.join(PKG_DIR, "..", "include", "ptxb200.h")
 
 GEMM_F32_OUT = 0x1
