@@ -40,10 +40,20 @@ WORKLOADS = {
     "c4": (8, 32, 8192, 128, True, 0.5, 20260004),
 }
 GEMM_WORKLOADS = {"c5": (8192, 8192, 8192, 20260005)}   # M, N (per GPU), K, seed; entries U[-1,1]
-# DRAM traffic of one C2 launch (dram__bytes_read.sum + dram__bytes_write.sum) from
-# the ncu capture summarised in profiles/fa_fwd_d128_c2.md; None until measured.
-NCU_TRAFFIC_BYTES = {"c2": None, "c3": None, "c4": None, "c5": None}
+# DRAM traffic of one launch (dram__bytes_read.sum + dram__bytes_write.sum) from the
+# ncu captures summarised in profiles/fa_fwd_d128_c2.md and profiles/gemm_bf16_c5.md;
+# None where no capture was taken.
+NCU_TRAFFIC_BYTES = {"c2": 201.38e6 + 42.33e6, "c3": None, "c4": None, "c5": 985.51e6 + 125.86e6}
 FALLBACK_PEAK_TFLOPS = 1590.0
+
+
+def host_threads():
+    """Host cores usable by this process (torchrun pins OMP_NUM_THREADS=1, so the CPU
+    legs ask the oracle for this many threads explicitly)."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
 
 
 def attn_flops(B, H, S, D, causal):
@@ -131,9 +141,9 @@ def cpu_sample(workload, n_slices, repeats=1):
     best = float("inf")
     for _ in range(repeats):
         t = time.perf_counter()
-        oracle.attention_ref_c(q, k, v, 1.0 / math.sqrt(D), causal)
+        oracle.attention_ref_c(q, k, v, 1.0 / math.sqrt(D), causal, nthreads=host_threads())
         best = min(best, time.perf_counter() - t)
-    return attn_flops(1, n_slices, S, D, causal) / best / 1e12, best, oracle.c_oracle_threads()
+    return attn_flops(1, n_slices, S, D, causal) / best / 1e12, best, host_threads()
 
 
 def run_reference_arm(args):
@@ -153,10 +163,10 @@ def run_reference_arm(args):
         rng = np.random.default_rng(seed)
         a, bt = (oracle.to_bf16_bits((rng.random((512, K)) * 2 - 1).astype(np.float32)) for _ in range(2))
         for _ in range(min(args.warmup, 2)):
-            oracle.gemm_ref_c(a, bt)
+            oracle.gemm_ref_c(a, bt, nthreads=host_threads())
         t0 = time.perf_counter()
         for _ in range(args.steps):
-            oracle.gemm_ref_c(a, bt)
+            oracle.gemm_ref_c(a, bt, nthreads=host_threads())
         dt = (time.perf_counter() - t0) / args.steps
         tflops = 2.0 * 512 * 512 * K / dt / 1e12
         sample = f"512 x 512 block of C over K={K} per step"
@@ -165,7 +175,7 @@ def run_reference_arm(args):
             "value": tflops, "unit": "TFLOPS", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic", "config": {"workload": f"{args.workload}: M={M} N={N} K={K}", "sample": sample},
-            "cpu_baseline": {"value": tflops, "unit": "TFLOPS", "cores": oracle.c_oracle_threads(), "kind": "port", "sample": sample},
+            "cpu_baseline": {"value": tflops, "unit": "TFLOPS", "cores": host_threads(), "kind": "port", "sample": sample},
             "e2e": {"value": tflops, "unit": "TFLOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}), flush=True)
         return
     B, H, S, D, causal, sigma, seed = WORKLOADS[args.workload]
@@ -174,17 +184,17 @@ def run_reference_arm(args):
                for s in (sigma, sigma, 1.0))
     scale = 1.0 / math.sqrt(D)
     t = time.perf_counter()
-    oracle.attention_ref_c(q[:1], k[:1], v[:1], scale, causal)
+    oracle.attention_ref_c(q[:1], k[:1], v[:1], scale, causal, nthreads=host_threads())
     t_slice = time.perf_counter() - t
     n_slices = int(max(1, min(4, 120.0 / (max(args.steps + args.warmup, 1) * t_slice))))
     for _ in range(args.warmup):
-        oracle.attention_ref_c(q[:n_slices], k[:n_slices], v[:n_slices], scale, causal)
+        oracle.attention_ref_c(q[:n_slices], k[:n_slices], v[:n_slices], scale, causal, nthreads=host_threads())
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        oracle.attention_ref_c(q[:n_slices], k[:n_slices], v[:n_slices], scale, causal)
+        oracle.attention_ref_c(q[:n_slices], k[:n_slices], v[:n_slices], scale, causal, nthreads=host_threads())
     dt = (time.perf_counter() - t0) / args.steps
     tflops = attn_flops(1, n_slices, S, D, causal) / dt / 1e12
-    threads = oracle.c_oracle_threads()
+    threads = host_threads()
     sample = f"{n_slices} of {B * H} (batch, head) slices of S={S} D={D} per step"
     line = {
         "impl": "reference", "metric": METRIC, "value": tflops, "unit": "TFLOPS", "n_gpus": args.gpus,
