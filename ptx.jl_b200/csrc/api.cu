@@ -133,7 +133,7 @@ const char* ptxb200_strerror(int code) {
         "?",            "gemm:empty",    "gemm:full",    "gemm:acc_empty", "gemm:acc_full",
         "fa:load.q_free", "fa:load.kv_free", "fa:mma.q_full", "fa:mma.kv_full", "fa:mma.p_full",
         "fa:mma.o_ready", "fa:softmax.s_full", "fa:corr.alpha", "fa:corr.l_ready",
-        "fa:corr.o_done", "probe",
+        "fa:corr.o_done", "probe", "-", "fa:shared memory base not 1024-byte aligned",
     };
     unsigned site = ((unsigned)code >> 8) & 0xFFu;
     const char* name = site < sizeof(sites) / sizeof(sites[0]) ? sites[site] : "?";

@@ -42,9 +42,14 @@ namespace ptxb200 {
 namespace {
 
 constexpr int kThreads = 512;
-constexpr int kRegsSoftmax = 184;
-constexpr int kRegsCorrection = 72;
-constexpr int kRegsOther = 72;
+#ifndef PTXB200_FA_REGS_SOFTMAX
+#define PTXB200_FA_REGS_SOFTMAX 168
+#define PTXB200_FA_REGS_CORRECTION 104
+#define PTXB200_FA_REGS_OTHER 72
+#endif
+constexpr int kRegsSoftmax = PTXB200_FA_REGS_SOFTMAX;
+constexpr int kRegsCorrection = PTXB200_FA_REGS_CORRECTION;
+constexpr int kRegsOther = PTXB200_FA_REGS_OTHER;
 static_assert(256 * kRegsSoftmax + 128 * kRegsCorrection + 128 * kRegsOther <= 65536,
               "register re-split must fit the register file");
 
@@ -57,6 +62,12 @@ static_assert(256 * kRegsSoftmax + 128 * kRegsCorrection + 128 * kRegsOther <= 6
 #define PTXB200_FA_EMU_MASK 0x0000u
 #endif
 constexpr uint32_t kEmuMask = PTXB200_FA_EMU_MASK;
+// The last 32 key columns of every tile are exponentiated by the correction warps
+// with the FMA-pipe polynomial, in parallel with the softmax warps' MUFU work on the
+// first 96: the softmax phase of a stage is latency-bound in a single warp per
+// scheduler, the correction warps' issue slots are otherwise idle, and the MUFU
+// pipe is co-critical with the tensor pipe.
+constexpr int kSoftmaxChunks = 3;   // 32-column chunks done by the softmax warps
 #ifndef PTXB200_FA_BATCH
 #define PTXB200_FA_BATCH 8
 #endif
@@ -67,6 +78,14 @@ enum : uint32_t {
   kSiteMmaPFull = 9, kSiteMmaOReady = 10, kSiteSoftmaxSFull = 11, kSiteCorrAlpha = 12,
   kSiteCorrLReady = 13, kSiteCorrODone = 14
 };
+
+// Unrolling of the MMA-issue thread's loops (its code runs once per tile, between
+// long stretches of other warps' code).
+#ifdef PTXB200_FA_MMA_ROLLED
+#define FA_MMA_UNROLL _Pragma("unroll 1")
+#else
+#define FA_MMA_UNROLL _Pragma("unroll")
+#endif
 
 // Timestamp hooks for offline latency studies; compiled out of the product build.
 #ifdef PTXB200_FA_TIMING
@@ -85,11 +104,14 @@ enum : uint32_t {
 template <int D>
 struct FaCfg {
   using T = AttnTile<D>;
-  static constexpr int kSlots = (D == 128) ? 4 : 8;           // K/V ring slots (one tile each)
+#ifndef PTXB200_FA_SLOTS128
+#define PTXB200_FA_SLOTS128 5
+#endif
+  static constexpr int kSlots = (D == 128) ? PTXB200_FA_SLOTS128 : 8;   // K/V ring slots (one tile each)
   static constexpr int kOffQ = 0;
   static constexpr int kOffKV = kOffQ + 2 * T::kTileBytes;
   static constexpr int kOffStats = kOffKV + kSlots * T::kTileBytes;  // alpha[2][128], l[2][128]
-  static constexpr int kOffBars = kOffStats + 4 * 128 * 4;
+  static constexpr int kOffBars = kOffStats + 4 * 128 * 4;   // basis[2][128], l[2][128]
   // barrier indices (8 bytes each)
   static constexpr int kBarQFull = 0;                  // [2]  TMA tx
   static constexpr int kBarQFree = 2;                  //      tcgen05.commit
@@ -104,7 +126,8 @@ struct FaCfg {
   static constexpr int kNumBars = kBarODone + 2;
   static constexpr int kOffTmemSlot = kOffBars + kNumBars * 8;
   static constexpr int kOffAbort = kOffTmemSlot + 8;
-  static constexpr int kSmemBytes = kOffAbort + 8 + 1024;  // + slack for manual alignment
+  static constexpr int kSmemBytes = kOffAbort + 8;   // the base must be 1024-byte aligned (checked)
+  static_assert(kSmemBytes <= 232448, "exceeds the 227 KiB a CTA can opt in to");
   static constexpr uint32_t kColS = 0;                 // + stage * 128
   static constexpr uint32_t kColO = 256;               // + stage * D
 };
@@ -122,14 +145,18 @@ struct FaParams {
   uint32_t* cta_flags;  // only read by the kCtaFlags variant: one word per CTA
 };
 
-// Work item -> (m_block, batch*head). Non-causal: m_block fastest, so CTAs that
-// run together share one head's K/V in L2 (flash_attention_defs.jl:80-82).
-// Causal: items sorted by decreasing length (m_block descending, slowest).
+// Work item -> (m_block, batch*head). m_block varies fastest, so CTAs that run
+// together share one head's K/V in L2 (flash_attention_defs.jl:80-82). Causal
+// items differ in length (2*m_block + 2 key tiles): within a head the longest come
+// first, and since the CTA count is not a multiple of the blocks per head, the
+// round-robin hands every CTA a mix of lengths. (Sorting all items by length
+// instead spread 148 different heads over the SMs at once and measured 5-8 %
+// slower: every CTA then streams its own K/V from HBM.)
 template <bool kCausal>
 __device__ __forceinline__ void decode_item(const FaParams& p, int w, int& mb, int& bh) {
   if (kCausal) {
-    mb = p.num_mblocks - 1 - w / p.bh;
-    bh = w % p.bh;
+    bh = w / p.num_mblocks;
+    mb = p.num_mblocks - 1 - (w % p.num_mblocks);
   } else {
     mb = w % p.num_mblocks;
     bh = w / p.num_mblocks;
@@ -155,14 +182,20 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
               const __grid_constant__ CUtensorMap tmap_v, const FaParams p) {
   using C = FaCfg<D>;
   using T = AttnTile<D>;
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  uint8_t* smem = smem_raw + (base - smem_u32(smem_raw));
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
+  const uint32_t base = smem_u32(smem_raw);
+  if ((base & 1023u) != 0) {
+    // the 128-byte swizzle needs 1024-byte aligned tiles; every thread leaves before
+    // any barrier or allocation exists
+    if (threadIdx.x == 0 && p.status != nullptr) atomicCAS(p.status, 0u, kStatusTimeoutTag | (17u << 8));
+    return;
+  }
 
   const uint32_t q_smem = base + C::kOffQ;
   const uint32_t kv_smem = base + C::kOffKV;
-  float* stats_alpha = reinterpret_cast<float*>(smem + C::kOffStats);          // [2][128]
-  float* stats_l = stats_alpha + 256;                                          // [2][128]
+  float* stats_neg = reinterpret_cast<float*>(smem + C::kOffStats);            // [2][128]
+  float* stats_l = stats_neg + 256;                                            // [2][128]
   const uint32_t bars = base + C::kOffBars;
   auto bar = [bars](int idx) -> uint32_t { return bars + 8u * (uint32_t)idx; };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + C::kOffTmemSlot);
@@ -184,7 +217,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar(C::kBarSFull + s), 1);
       mbar_init(bar(C::kBarPFull + 2 * s + 0), 128);
-      mbar_init(bar(C::kBarPFull + 2 * s + 1), 128);
+      mbar_init(bar(C::kBarPFull + 2 * s + 1), 256);   // softmax warps + correction warps
       mbar_init(bar(C::kBarAlpha + s), 128);
       mbar_init(bar(C::kBarLReady + s), 128);
       mbar_init(bar(C::kBarOReady + s), 128);
@@ -216,8 +249,12 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
           const uint32_t s = kv_it % C::kSlots;
           const uint32_t ph = (kv_it / C::kSlots) & 1u;
           mbar_wait(bar(C::kBarKvFree + s), ph ^ 1u, wctx, kSiteLoadKvFree);
+#if defined(PTXB200_FA_ABLATE) && PTXB200_FA_ABLATE == 7
+          mbar_arrive(bar(C::kBarKvFull + s));   // no data movement: measures everything but the loads
+#else
           mbar_arrive_expect_tx(bar(C::kBarKvFull + s), T::kTileBytes);
           T::load(kv_smem + s * T::kTileBytes, tmap, row, bar(C::kBarKvFull + s));
+#endif
           ++kv_it;
         };
         for (int w = blockIdx.x; w < p.total_work; w += gridDim.x, ++item_i) {
@@ -234,7 +271,9 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
           mbar_arrive_expect_tx(bar(C::kBarQFull + 1), T::kTileBytes);
           T::load(q_smem + T::kTileBytes, &tmap_q, q_row0 + kAttnRows, bar(C::kBarQFull + 1));
           for (int j = 0; j < nt1; ++j) {
+            FA_TSTAMP(w == 0, 3, j, 0);
             kv_load(&tmap_v, kv_row0 + j * kAttnRows);
+            FA_TSTAMP(w == 0, 3, j, 1);
             if (j + 1 < nt1) kv_load(&tmap_k, kv_row0 + (j + 1) * kAttnRows);
           }
         }
@@ -254,7 +293,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
         auto qk = [&](int stage, uint32_t kslot) {   // S_stage = Q_stage K^T
           const uint32_t qa = q_smem + stage * T::kTileBytes;
           const uint32_t ka = kv_smem + kslot * T::kTileBytes;
-#pragma unroll
+FA_MMA_UNROLL
           for (int kk = 0; kk < T::kQKAtoms; ++kk)
 #if defined(PTXB200_FA_ABLATE) && (PTXB200_FA_ABLATE == 5 || PTXB200_FA_ABLATE == 6)
             if (kk < 0)
@@ -268,12 +307,12 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
         // exponentiated (the reference's split-P idea, flash_attention_defs.jl:36-50).
         auto pv = [&](int stage, uint32_t vslot, bool accumulate, uint32_t parity) {
           const uint32_t va = kv_smem + vslot * T::kTileBytes;
-#pragma unroll
+FA_MMA_UNROLL
           for (int h = 0; h < 2; ++h) {
             mbar_wait(bar(C::kBarPFull + 2 * stage + h), parity, wctx, kSiteMmaPFull);
             if (h == 0) mbar_wait(bar(C::kBarOReady + stage), parity, wctx, kSiteMmaOReady);
             tc_fence_after();
-#pragma unroll
+FA_MMA_UNROLL
             for (int kk = 4 * h; kk < 4 * h + 4; ++kk)
 #if defined(PTXB200_FA_ABLATE) && (PTXB200_FA_ABLATE == 4 || PTXB200_FA_ABLATE == 6)
               if (kk < 0)
@@ -304,7 +343,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
             uint32_t kslot = 0;
             if (has_next) kslot = kv_wait();
             FA_TSTAMP(w == 0, 2, j, 7);
-#pragma unroll
+FA_MMA_UNROLL
             for (int s = 0; s < 2; ++s) {
               if (j < nt[s]) {
                 FA_TSTAMP(w == 0, 2, j, 3 * s + 0);
@@ -353,6 +392,14 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
         ++cnt_s;
         tc_fence_after();
         FA_TSTAMP(w == 0 && row == 0, stage, j, 1);
+#if defined(PTXB200_FA_ABLATE) && PTXB200_FA_ABLATE == 8
+        stats_neg[stage * 128 + row] = 0.0f;
+        mbar_arrive(bar(C::kBarAlpha + stage));
+        tc_fence_before();
+        mbar_arrive(bar(C::kBarPFull + 2 * stage + 0));
+        mbar_arrive(bar(C::kBarPFull + 2 * stage + 1));
+        continue;
+#endif
         uint32_t v[4][32];
 #pragma unroll
         for (int c = 0; c < 4; ++c) tmem_ld32(t_row + c * 32, v[c]);
@@ -380,27 +427,29 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
         }
         const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
 
+        float alpha = 1.0f;
         if (j == 0) {
           m_run = m_tile;
         } else {
-          float alpha = 1.0f;
           const float m_new = fmaxf(m_run, m_tile);
           if ((m_new - m_run) * scale_log2 > p.rescale_threshold) {
             alpha = ex2_approx((m_run - m_new) * scale_log2);
             m_run = m_new;
           }
-          stats_alpha[stage * 128 + row] = alpha;
-          mbar_arrive(bar(C::kBarAlpha + stage));
           l_run *= alpha;
         }
+        const float neg = -m_run * scale_log2;
+        // the basis goes to the correction warps: they exponentiate their share of the
+        // columns against it and derive the O rescale factor from its change
+        stats_neg[stage * 128 + row] = neg;
+        mbar_arrive(bar(C::kBarAlpha + stage));
 
         FA_TSTAMP(w == 0 && row == 0, stage, j, 3);
-        const float neg = -m_run * scale_log2;
         const float2 scale2 = make_float2(scale_log2, scale_log2);
         const float2 neg2 = make_float2(neg, neg);
         float2 sum2[2] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)};
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < kSoftmaxChunks; ++c) {
           uint32_t pk[16];
           // batches of kBatch pairs: all scaled inputs, then all exponentials back to
           // back (so the MUFU latency of one is hidden behind the issue of the next),
@@ -438,8 +487,8 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
             }
           }
           tmem_st16(t_row + c * 16, pk);
-          if (c & 1) {
-            // one 64-column half of P is in tensor memory: publish it
+          if (c == 1 || c == kSoftmaxChunks - 1) {
+            // this warp's share of a 64-column half of P is in tensor memory: publish it
             tc_wait_st();
             tc_fence_before();
             mbar_arrive(bar(C::kBarPFull + 2 * stage + (c >> 1)));
@@ -462,36 +511,77 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
     mbar_arrive(bar(C::kBarOReady + 0));   // O is free for the first item
     mbar_arrive(bar(C::kBarOReady + 1));
     uint32_t cnt_a[2] = {0, 0};
+    uint32_t cnt_h[2] = {0, 0};   // S tiles seen per stage
     uint32_t item_i = 0;
     for (int w = blockIdx.x; w < p.total_work; w += gridDim.x, ++item_i) {
       int mb, bh, nt[2];
       decode_item<kCausal>(p, w, mb, bh);
       tile_counts<kCausal>(p, mb, nt[0], nt[1]);
       const int nt_max = nt[1];
+      float l_part[2] = {0.0f, 0.0f};   // row sums of the columns this thread exponentiates
+      float neg_prev[2] = {0.0f, 0.0f};
 #pragma unroll 1
-      for (int j = 1; j < nt_max; ++j) {
+      for (int j = 0; j < nt_max; ++j) {
 #pragma unroll
         for (int s = 0; s < 2; ++s) {
           if (j < nt[s]) {
+            uint32_t sv[32];
+            [[maybe_unused]] const bool diag = kCausal && j == nt[s] - 1;
+            {
+              // fetch this row's last 32 scores while the softmax warp forms the maximum
+              mbar_wait(bar(C::kBarSFull + s), cnt_h[s] & 1u, wctx, kSiteSoftmaxSFull);
+              ++cnt_h[s];
+              tc_fence_after();
+              tmem_ld32(t_lane + C::kColS + s * 128 + 96, sv);
+              tc_wait_ld_bind(sv);
+            }
             mbar_wait(bar(C::kBarAlpha + s), cnt_a[s] & 1u, wctx, kSiteCorrAlpha);
             ++cnt_a[s];
-            const float alpha = stats_alpha[s * 128 + row];
-            if (__any_sync(0xffffffffu, alpha != 1.0f)) {
-              tc_fence_after();
+            const float neg = stats_neg[s * 128 + row];
+            // alpha = 2^((m_old - m_new) * c) = 2^(neg_new - neg_old); exactly 1 when the basis stood
+            const float alpha = (j == 0 || neg == neg_prev[s]) ? 1.0f : ex2_approx(neg - neg_prev[s]);
+            neg_prev[s] = neg;
+            if (j > 0) {
+              if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+                tc_fence_after();
 #pragma unroll 1
-              for (int c = 0; c < D / 32; ++c) {
-                uint32_t o[32];
-                const uint32_t a = t_lane + C::kColO + s * D + c * 32;
-                tmem_ld32(a, o);
-                tc_wait_ld_bind(o);
+                for (int c = 0; c < D / 32; ++c) {
+                  uint32_t o[32];
+                  const uint32_t a = t_lane + C::kColO + s * D + c * 32;
+                  tmem_ld32(a, o);
+                  tc_wait_ld_bind(o);
 #pragma unroll
-                for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                tmem_st32(a, o);
+                  for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                  tmem_st32(a, o);
+                }
+                tc_wait_st();
               }
-              tc_wait_st();
+              tc_fence_before();
+              mbar_arrive(bar(C::kBarOReady + s));
             }
-            tc_fence_before();
-            mbar_arrive(bar(C::kBarOReady + s));
+            {
+              const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
+              const float2 neg2 = make_float2(neg, neg);
+              float2 sum2 = make_float2(0.0f, 0.0f);
+              uint32_t pk[16];
+#pragma unroll
+              for (int i = 0; i < 16; ++i) {
+                float2 e = exp2_poly2(__ffma2_rn(
+                    make_float2(__uint_as_float(sv[2 * i]), __uint_as_float(sv[2 * i + 1])), scale2, neg2));
+                if (kCausal) {
+                  // diagonal tile: keys above the diagonal weigh exactly zero
+                  if (diag && 96 + 2 * i > row) e.x = 0.0f;
+                  if (diag && 96 + 2 * i + 1 > row) e.y = 0.0f;
+                }
+                sum2 = __fadd2_rn(sum2, e);
+                pk[i] = pack_bf16x2(e.x, e.y);
+              }
+              tmem_st16(t_lane + C::kColS + s * 128 + 48, pk);   // P columns of keys 96..127
+              tc_wait_st();
+              tc_fence_before();
+              mbar_arrive(bar(C::kBarPFull + 2 * s + 1));
+              l_part[s] = l_part[s] * alpha + (sum2.x + sum2.y);
+            }
           }
         }
       }
@@ -502,7 +592,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
         mbar_wait(bar(C::kBarODone + s), item_i & 1u, wctx, kSiteCorrODone);
         mbar_wait(bar(C::kBarLReady + s), item_i & 1u, wctx, kSiteCorrLReady);
         tc_fence_after();
-        const float inv_l = 1.0f / stats_l[s * 128 + row];
+        const float inv_l = 1.0f / (stats_l[s * 128 + row] + l_part[s]);
         __nv_bfloat16* dst = p.o + (size_t)(q_row0 + s * kAttnRows + row) * D;
 #pragma unroll 1
         for (int c = 0; c < D / 32; ++c) {

@@ -170,9 +170,7 @@ __device__ __forceinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, co
 }
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtx& ctx,
                                           uint32_t site) {
-#pragma unroll 1
-  for (int i = 0; i < 16; ++i)
-    if (mbar_try_wait(bar, parity)) return true;
+  if (mbar_try_wait(bar, parity)) return true;   // already complete: the common case on hot paths
   return mbar_wait_slow(bar, parity, ctx, site);
 }
 
