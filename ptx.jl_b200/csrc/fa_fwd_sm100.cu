@@ -75,7 +75,7 @@ constexpr int kBatch = PTXB200_FA_BATCH;   // element pairs per exp batch
 
 enum : uint32_t {
   kSiteLoadQFree = 5, kSiteLoadKvFree = 6, kSiteMmaQFull = 7, kSiteMmaKvFull = 8,
-  kSiteMmaPFull = 9, kSiteMmaOReady = 10, kSiteSoftmaxSFull = 11, kSiteCorrAlpha = 12,
+  kSiteMmaPFull = 9, kSiteSoftmaxSFull = 11, kSiteCorrAlpha = 12,
   kSiteCorrLReady = 13, kSiteCorrODone = 14
 };
 
@@ -121,8 +121,7 @@ struct FaCfg {
   static constexpr int kBarPFull = kBarSFull + 2;      // [2 stages][2 halves] 128 softmax threads
   static constexpr int kBarAlpha = kBarPFull + 4;      // [2] 128 softmax threads
   static constexpr int kBarLReady = kBarAlpha + 2;     // [2] 128 softmax threads
-  static constexpr int kBarOReady = kBarLReady + 2;    // [2] 128 correction threads
-  static constexpr int kBarODone = kBarOReady + 2;     // [2] tcgen05.commit
+  static constexpr int kBarODone = kBarLReady + 2;     // [2] tcgen05.commit
   static constexpr int kNumBars = kBarODone + 2;
   static constexpr int kOffTmemSlot = kOffBars + kNumBars * 8;
   static constexpr int kOffAbort = kOffTmemSlot + 8;
@@ -216,11 +215,10 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar(C::kBarSFull + s), 1);
-      mbar_init(bar(C::kBarPFull + 2 * s + 0), 128);
+      mbar_init(bar(C::kBarPFull + 2 * s + 0), 256);   // softmax warps (P half 0) + correction warps (O ready)
       mbar_init(bar(C::kBarPFull + 2 * s + 1), 256);   // softmax warps + correction warps
       mbar_init(bar(C::kBarAlpha + s), 128);
       mbar_init(bar(C::kBarLReady + s), 128);
-      mbar_init(bar(C::kBarOReady + s), 128);
       mbar_init(bar(C::kBarODone + s), 1);
     }
     mbar_fence_init();
@@ -310,7 +308,6 @@ FA_MMA_UNROLL
 FA_MMA_UNROLL
           for (int h = 0; h < 2; ++h) {
             mbar_wait(bar(C::kBarPFull + 2 * stage + h), parity, wctx, kSiteMmaPFull);
-            if (h == 0) mbar_wait(bar(C::kBarOReady + stage), parity, wctx, kSiteMmaOReady);
             tc_fence_after();
 FA_MMA_UNROLL
             for (int kk = 4 * h; kk < 4 * h + 4; ++kk)
@@ -508,8 +505,8 @@ FA_MMA_UNROLL
     setmaxnreg_dec<kRegsCorrection>();
     const int row = tid & 127;
     const uint32_t t_lane = tmem_addr(tmem, (warp & 3) * 32, 0);
-    mbar_arrive(bar(C::kBarOReady + 0));   // O is free for the first item
-    mbar_arrive(bar(C::kBarOReady + 1));
+    mbar_arrive(bar(C::kBarPFull + 0));   // O is free for the first item
+    mbar_arrive(bar(C::kBarPFull + 2));
     uint32_t cnt_a[2] = {0, 0};
     uint32_t cnt_h[2] = {0, 0};   // S tiles seen per stage
     uint32_t item_i = 0;
@@ -557,7 +554,7 @@ FA_MMA_UNROLL
                 tc_wait_st();
               }
               tc_fence_before();
-              mbar_arrive(bar(C::kBarOReady + s));
+              mbar_arrive(bar(C::kBarPFull + 2 * s));
             }
             {
               const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
@@ -602,7 +599,7 @@ FA_MMA_UNROLL
           if (c == D / 32 - 1) {
             // last read of O_s: the next item may overwrite it
             tc_fence_before();
-            mbar_arrive(bar(C::kBarOReady + s));
+            mbar_arrive(bar(C::kBarPFull + 2 * s));
           }
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
