@@ -130,19 +130,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     }
   } else if (warp == 1) {
     // ---------------- MMA issue ----------------
-    if (elect_one()) {
+    // The whole warp walks the loop converged; the tcgen05 instructions elect their
+    // issuing lane themselves (see tc_mma_ss_warp).
+    {
       constexpr uint32_t idesc = make_idesc_bf16_f32(kBM, kBN, false, false);
       uint32_t it = 0, t = 0;
       for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++t) {
         const uint32_t buf = t & 1u;
         const uint32_t aph = (t >> 1) & 1u;
-        mbar_wait(bar_acc_empty + 8 * buf, aph ^ 1u, wctx, kSiteAccEmpty);
+        mbar_wait_warp(bar_acc_empty + 8 * buf, aph ^ 1u, wctx, kSiteAccEmpty);
         tc_fence_after();
         const uint32_t d_tmem = tmem + buf * kAccCols;
         for (int k = 0; k < kiters; ++k, ++it) {
           const uint32_t s = it % kStages;
           const uint32_t ph = (it / kStages) & 1u;
-          mbar_wait(bar_full + 8 * s, ph, wctx, kSiteFull);
+          mbar_wait_warp(bar_full + 8 * s, ph, wctx, kSiteFull);
           tc_fence_after();
           const uint32_t da = sdesc_lo(a_base + s * kAStageBytes, 16);
           const uint32_t db = sdesc_lo(b_base + s * kBStageBytes, 16);
@@ -150,11 +152,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 #pragma unroll
           for (int kk = 0; kk < kBK / 16; ++kk) {
             // +32 bytes (2 descriptor units) per 16-element K step inside the swizzle row
-            tc_mma_ss(d_tmem, da + 2 * kk, dhi, db + 2 * kk, dhi, idesc, (k | kk) != 0 ? 1u : 0u);
+            tc_mma_ss_warp(d_tmem, da + 2 * kk, dhi, db + 2 * kk, dhi, idesc, (k | kk) != 0 ? 1u : 0u);
           }
-          tc_commit(bar_empty + 8 * s);   // slot free once these MMAs have read it
+          tc_commit_warp(bar_empty + 8 * s);   // slot free once these MMAs have read it
         }
-        tc_commit(bar_acc_full + 8 * buf);  // accumulator complete
+        tc_commit_warp(bar_acc_full + 8 * buf);  // accumulator complete
       }
     }
   } else {

@@ -255,6 +255,54 @@ __device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint
       : "memory");
 }
 
+// Bounded wait for a whole converged warp: every lane polls once and the warp
+// branches on the vote (a uniform branch: no divergence bookkeeping on the hot
+// path); only if the phase is not complete yet does lane 0 run the bounded loop.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, const WaitCtx& ctx,
+                                               uint32_t site) {
+  if (__all_sync(0xffffffffu, mbar_try_wait(bar, parity))) return true;
+  bool ok = true;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait_slow(bar, parity, ctx, site);
+  return __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+}
+
+// Warp-level forms: EVERY lane of a converged warp calls these with identical
+// operands; one elected lane issues the instruction. tcgen05.mma / commit are
+// warp-scope, uniform-datapath instructions: issued from a converged warp with the
+// election inside the instruction's predicate, the descriptors stay in uniform
+// registers and an MMA costs a few issue cycles; issued by one diverged thread
+// (an `if (lane == 0)` around the whole loop) each MMA costs ~50 cycles of that
+// thread. In isolation that is 2150 vs 2650 cycles per pair of attention tiles; in
+// the attention kernel itself, next to seven busy warps per scheduler, the converged
+// form measured slower, so only the GEMM uses these.
+__device__ __forceinline__ void tc_mma_ss_warp(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi,
+                                               uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t.reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+      "setp.ne.b32 p, %6, 0;\n\telect.sync _|q, 0xffffffff;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}" ::"r"(d_tmem),
+      "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tc_mma_ts_warp(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo,
+                                               uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t.reg .b64 db;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "setp.ne.b32 p, %5, 0;\n\telect.sync _|q, 0xffffffff;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}" ::"r"(d_tmem),
+      "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tc_commit_warp(uint32_t bar) {
+  asm volatile(
+      "{\n\t.reg .pred q;\n\telect.sync _|q, 0xffffffff;\n\t"
+      "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(bar)
+      : "memory");
+}
+
 // ---------------------------------------------------------------------------
 // TMEM <-> registers, 32 lanes x 32-bit shape: the executing warp touches lanes
 // 32*(warp_id % 4) .. +31, thread i <-> lane i, register k <-> column k.
