@@ -15,15 +15,28 @@
 //     2^8 (the slack cancels exactly in the final O / l);
 //   * head dim 64 and 128, causal and non-causal, from one template;
 //   * causal work items skip the key tiles above the diagonal per 128-row stage,
-//     mask only the diagonal tile, and are handed out longest first;
-//   * a protocol of single-producer/single-consumer mbarrier phases in which no
-//     producer can run two phases ahead of its consumer (argued per barrier
-//     below), so no padding commits and no split-by-parity barriers are needed;
+//     mask only the diagonal tile, and are handed out longest first within a head;
+//   * the exponentials of a tile are split between two warps and two pipes: the
+//     stage's softmax warp does key columns 0-95 on the MUFU, the correction warp
+//     of the same rows does columns 96-127 with a polynomial on the FMA pipe;
+//   * a protocol of mbarrier phases in which no producer can run two phases ahead
+//     of its consumer: each producer's next arrival is downstream of an MMA issue
+//     that waited for the consumer's previous arrival, so no padding commits, no
+//     split-by-parity barriers and no "slot free" barriers are needed;
 //   * every wait is bounded and reports to a status word.
 //
 // Roles (512 threads): warps 0-3 / 4-7 softmax of stage 0 / 1 (thread = one row),
-// warps 8-11 correction + epilogue, warp 12 MMA issue, warp 13 TMA loads,
-// warps 14-15 idle (they only take part in the register re-split).
+// warps 8-11 correction (O rescale, their share of the exponentials, epilogue),
+// warp 12 MMA issue, warp 13 TMA loads, warps 14-15 idle (they only take part in
+// the register re-split).
+//
+// Barriers: q_full[2], q_free, kv_full[n], kv_free[n] (TMA ring); s_full[2] (MMA ->
+// softmax and correction warps); basis[2] (softmax -> correction, every tile: the
+// row's basis -m*c, from whose change the O rescale factor follows);
+// p_full[stage][half]: half 0 completes with 128 softmax arrivals (P columns 0-31
+// stored) plus 128 correction arrivals (O rescaled for this tile, or free after the
+// previous item's epilogue), half 1 with 128 softmax arrivals (columns 32-47) plus
+// 128 correction arrivals (columns 48-63); l_ready[2], o_done[2] (end of item).
 //
 // Tensor memory (512 columns x 128 lanes of 32 bit):
 //   S0 at 0, S1 at 128 (fp32, 128 columns each; P_s overwrites the first 64
@@ -118,8 +131,8 @@ struct FaCfg {
   static constexpr int kBarKvFull = 3;                 // [kSlots] TMA tx
   static constexpr int kBarKvFree = kBarKvFull + kSlots;   // [kSlots] tcgen05.commit
   static constexpr int kBarSFull = kBarKvFree + kSlots;    // [2] tcgen05.commit
-  static constexpr int kBarPFull = kBarSFull + 2;      // [2 stages][2 halves] 128 softmax threads
-  static constexpr int kBarAlpha = kBarPFull + 4;      // [2] 128 softmax threads
+  static constexpr int kBarPFull = kBarSFull + 2;      // [2 stages][2 halves] 128 softmax + 128 correction threads
+  static constexpr int kBarAlpha = kBarPFull + 4;      // [2] basis published: 128 softmax threads
   static constexpr int kBarLReady = kBarAlpha + 2;     // [2] 128 softmax threads
   static constexpr int kBarODone = kBarLReady + 2;     // [2] tcgen05.commit
   static constexpr int kNumBars = kBarODone + 2;
@@ -500,8 +513,11 @@ FA_MMA_UNROLL
     if (p.dbg != nullptr && blockIdx.x == 0 && row == 0) p.dbg[6 + stage] = cnt_s;
   } else {
     // =====================================================================
-    // correction (rescale O when a row maximum moved) + epilogue
+    // correction warps: rescale O when a row maximum moved, exponentiate key
+    // columns 96-127 of every tile on the FMA pipe, and run the epilogue
     // =====================================================================
+    // 104 registers is below the 128 the kernel launches with: a release, like the
+    // MMA/load warpgroup's, that the two softmax warpgroups' increase draws on
     setmaxnreg_dec<kRegsCorrection>();
     const int row = tid & 127;
     const uint32_t t_lane = tmem_addr(tmem, (warp & 3) * 32, 0);
