@@ -102,6 +102,22 @@ int fa_fwd_bf16(void* O, const void* Q, const void* K, const void* V, int B, int
                 float sm_scale, int causal, unsigned flags, void* dbg, void* stream);
 
 /*
+ * fa_fwd_bf16 with two additions next to the reference's path (its kernel has
+ * neither: one K/V head per query head, no statistics output --
+ * flash_attention_defs.jl:621-630):
+ *   H_kv  number of key/value heads per batch entry; must divide H. Query head h
+ *         attends to key/value head h / (H / H_kv) (grouped-query attention).
+ *         K and V are [B, H_kv, S, D].
+ *   lse   NULL, or B*H*S floats on the device that receive, per query row,
+ *         log(sum_j exp(q.k_j * sm_scale)) over the kept keys (natural log) --
+ *         what a backward pass or a split-sequence combine needs.
+ * Everything else as fa_fwd_bf16 (which is this call with lse = NULL, H_kv = H).
+ */
+int fa_fwd_bf16_ex(void* O, void* lse, const void* Q, const void* K, const void* V, int B, int H,
+                   int H_kv, int S, int D, float sm_scale, int causal, unsigned flags, void* dbg,
+                   void* stream);
+
+/*
  * fa_fwd_bf16 without any allocation. (No counterpart in the reference: its
  * launch closure allocates nothing per call either, but its set-up uploads three
  * descriptor blobs into freshly allocated device memory.)

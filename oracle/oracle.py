@@ -58,6 +58,19 @@ def attention_ref_numpy(Q: np.ndarray, K: np.ndarray, V: np.ndarray, sm_scale: f
     return ((ex / ex.sum(axis=1, keepdims=True, dtype=np.float32)) @ Vb).astype(np.float32)
 
 
+def attention_lse_numpy(Q: np.ndarray, K: np.ndarray, sm_scale: float, causal: bool = False) -> np.ndarray:
+    """Per query row log(sum_j exp(q.k_j * sm_scale)) over the kept keys, float64 on
+    bf16-quantised inputs: the row statistic behind fab_cpu_ref's normalisation
+    (rmax + log(sum(ex)) in test/gpu/blackwell/flash_attention_defs.jl:972-975)."""
+    Qb, Kb = _quantise(Q).astype(np.float64), _quantise(K).astype(np.float64)
+    scores = (Qb @ Kb.T) * float(sm_scale)
+    if causal:
+        S = scores.shape[0]
+        scores = np.where(np.triu(np.ones((S, S), dtype=bool), k=1), -np.inf, scores)
+    rmax = scores.max(axis=1, keepdims=True)
+    return (rmax[:, 0] + np.log(np.exp(scores - rmax).sum(axis=1))).astype(np.float32)
+
+
 def gemm_ref_numpy(A: np.ndarray, B: np.ndarray) -> np.ndarray:
     """A (M,K), B (K,N) fp32 -> fp32 (M,N) on bf16-quantised inputs."""
     return (_quantise(A) @ _quantise(B)).astype(np.float32)

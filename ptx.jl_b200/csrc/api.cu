@@ -161,22 +161,28 @@ int gemm_bf16(void* C, const void* A, const void* Bt, int M, int N, int K, int l
   return launch_gemm(*ctx, C, A, Bt, M, N, K, ldc, flags, (cudaStream_t)stream);
 }
 
-int fa_fwd_bf16(void* O, const void* Q, const void* K, const void* V, int B, int H, int S, int D,
-                float sm_scale, int causal, unsigned flags, void* dbg, void* stream) {
+int fa_fwd_bf16_ex(void* O, void* lse, const void* Q, const void* K, const void* V, int B, int H,
+                   int H_kv, int S, int D, float sm_scale, int causal, unsigned flags, void* dbg,
+                   void* stream) {
   if (O == nullptr || Q == nullptr || K == nullptr || V == nullptr) return PTXB200_E_INVALID;
-  if (B <= 0 || H <= 0 || S <= 0 || D <= 0) return PTXB200_E_INVALID;
+  if (B <= 0 || H <= 0 || H_kv <= 0 || S <= 0 || D <= 0) return PTXB200_E_INVALID;
   if (causal != 0 && causal != 1) return PTXB200_E_INVALID;
   if (flags & ~PTXB200_FA_NO_LAZY_RESCALE) return PTXB200_E_INVALID;
   if (!(sm_scale > 0.0f) || !(sm_scale < 1e30f)) return PTXB200_E_INVALID;
-  if ((D != 64 && D != 128) || S % 256 != 0) return PTXB200_E_SHAPE;
+  if ((D != 64 && D != 128) || S % 256 != 0 || H % H_kv != 0) return PTXB200_E_SHAPE;
   if ((long long)B * H * S >= (1ll << 31)) return PTXB200_E_SHAPE;
   if (!aligned16(O) || !aligned16(Q) || !aligned16(K) || !aligned16(V)) return PTXB200_E_ALIGN;
-  if (dbg != nullptr && !aligned16(dbg)) return PTXB200_E_ALIGN;
+  if ((dbg != nullptr && !aligned16(dbg)) || (lse != nullptr && !aligned16(lse))) return PTXB200_E_ALIGN;
   DeviceCtx* ctx = nullptr;
   int rc = current_ctx(&ctx);
   if (rc != PTXB200_OK) return rc;
-  return launch_fa_fwd(*ctx, O, Q, K, V, B, H, S, D, sm_scale, causal, flags, dbg,
+  return launch_fa_fwd(*ctx, O, lse, Q, K, V, B, H, H_kv, S, D, sm_scale, causal, flags, dbg,
                        ctx->workspace + kWsStatus, (cudaStream_t)stream);
+}
+
+int fa_fwd_bf16(void* O, const void* Q, const void* K, const void* V, int B, int H, int S, int D,
+                float sm_scale, int causal, unsigned flags, void* dbg, void* stream) {
+  return fa_fwd_bf16_ex(O, nullptr, Q, K, V, B, H, H, S, D, sm_scale, causal, flags, dbg, stream);
 }
 
 int ptxb200_sync_status(void* stream) {

@@ -155,6 +155,9 @@ struct FaParams {
   uint32_t* status;
   uint32_t* dbg;
   uint32_t* cta_flags;  // only read by the kCtaFlags variant: one word per CTA
+  float* lse;           // optional: log-sum-exp of the scaled scores per query row
+  int heads_q;          // query heads per batch entry
+  int heads_kv;         // key/value heads per batch entry (divides heads_q)
 };
 
 // Work item -> (m_block, batch*head). m_block varies fastest, so CTAs that run
@@ -272,8 +275,11 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
           int mb, bh, nt0, nt1;
           decode_item<kCausal>(p, w, mb, bh);
           tile_counts<kCausal>(p, mb, nt0, nt1);
-          const int kv_row0 = bh * p.seqlen;
-          const int q_row0 = kv_row0 + mb * 2 * kAttnRows;
+          // grouped heads: query head h reads key/value head h / (heads_q / heads_kv)
+          const int b_idx = bh / p.heads_q;
+          const int kv_head = (bh - b_idx * p.heads_q) / (p.heads_q / p.heads_kv);
+          const int kv_row0 = (b_idx * p.heads_kv + kv_head) * p.seqlen;
+          const int q_row0 = bh * p.seqlen + mb * 2 * kAttnRows;
           // Q may be overwritten once every S = Q K^T of the previous item has run
           mbar_wait(bar(C::kBarQFree), (item_i & 1u) ^ 1u, wctx, kSiteLoadQFree);
           mbar_arrive_expect_tx(bar(C::kBarQFull + 0), T::kTileBytes);
@@ -605,7 +611,12 @@ FA_MMA_UNROLL
         mbar_wait(bar(C::kBarODone + s), item_i & 1u, wctx, kSiteCorrODone);
         mbar_wait(bar(C::kBarLReady + s), item_i & 1u, wctx, kSiteCorrLReady);
         tc_fence_after();
-        const float inv_l = 1.0f / (stats_l[s * 128 + row] + l_part[s]);
+        const float l_total = stats_l[s * 128 + row] + l_part[s];
+        const float inv_l = 1.0f / l_total;
+        if (p.lse != nullptr) {
+          // sum_j 2^(s_j c) = 2^(m c) * l with basis -m c in neg_prev: natural log of it
+          p.lse[q_row0 + s * kAttnRows + row] = (log2f(l_total) - neg_prev[s]) * 0.6931471805599453f;
+        }
         __nv_bfloat16* dst = p.o + (size_t)(q_row0 + s * kAttnRows + row) * D;
 #pragma unroll 1
         for (int c = 0; c < D / 32; ++c) {
@@ -665,15 +676,16 @@ int launch_variant(const DeviceCtx& ctx, const CUtensorMap& tq, const CUtensorMa
 
 }  // namespace
 
-int launch_fa_fwd(const DeviceCtx& ctx, void* O, const void* Q, const void* K, const void* V,
-                  int B, int H, int S, int D, float sm_scale, int causal, unsigned flags,
-                  void* dbg, uint32_t* status, cudaStream_t stream) {
+int launch_fa_fwd(const DeviceCtx& ctx, void* O, void* lse, const void* Q, const void* K,
+                  const void* V, int B, int H, int H_kv, int S, int D, float sm_scale, int causal,
+                  unsigned flags, void* dbg, uint32_t* status, cudaStream_t stream) {
   const uint64_t rows = (uint64_t)B * H * S;
+  const uint64_t rows_kv = (uint64_t)B * H_kv * S;
   CUtensorMap tq, tk, tv;
   int rc;
   if ((rc = encode_tmap_bf16_2d(&tq, Q, rows, D, (uint64_t)D * 2, 128, 64)) != PTXB200_OK) return rc;
-  if ((rc = encode_tmap_bf16_2d(&tk, K, rows, D, (uint64_t)D * 2, 128, 64)) != PTXB200_OK) return rc;
-  if ((rc = encode_tmap_bf16_2d(&tv, V, rows, D, (uint64_t)D * 2, 128, 64)) != PTXB200_OK) return rc;
+  if ((rc = encode_tmap_bf16_2d(&tk, K, rows_kv, D, (uint64_t)D * 2, 128, 64)) != PTXB200_OK) return rc;
+  if ((rc = encode_tmap_bf16_2d(&tv, V, rows_kv, D, (uint64_t)D * 2, 128, 64)) != PTXB200_OK) return rc;
   FaParams p;
   p.o = reinterpret_cast<__nv_bfloat16*>(O);
   p.seqlen = S;
@@ -685,6 +697,9 @@ int launch_fa_fwd(const DeviceCtx& ctx, void* O, const void* Q, const void* K, c
   p.status = status;
   p.dbg = reinterpret_cast<uint32_t*>(dbg);
   p.cta_flags = nullptr;
+  p.lse = reinterpret_cast<float*>(lse);
+  p.heads_q = H;
+  p.heads_kv = H_kv;
   if (D == 128) {
     return causal ? launch_variant<128, true>(ctx, tq, tk, tv, p, stream)
                   : launch_variant<128, false>(ctx, tq, tk, tv, p, stream);
@@ -816,6 +831,9 @@ extern "C" int fa_fwd_bf16_noalloc(void* O, const void* Q, const void* K, const 
   p.status = nd.scratch;
   p.dbg = nullptr;
   p.cta_flags = nd.scratch + kNoAllocFlagBase;
+  p.lse = nullptr;
+  p.heads_q = H;
+  p.heads_kv = H;
   const int grid = p.total_work < nd.sm_count ? p.total_work : nd.sm_count;
   if (grid > kNoAllocMaxCtas) {
     set_error_text("fa_fwd_bf16_noalloc: launch needs more CTAs than the 240 flag slots of the "

@@ -59,9 +59,9 @@ int encode_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t rows, uint6
 // Kernel launchers (one per .cu file).
 int launch_gemm(const DeviceCtx& ctx, void* C, const void* A, const void* Bt, int M, int N, int K,
                 int ldc, unsigned flags, cudaStream_t stream);
-int launch_fa_fwd(const DeviceCtx& ctx, void* O, const void* Q, const void* K, const void* V,
-                  int B, int H, int S, int D, float sm_scale, int causal, unsigned flags,
-                  void* dbg, uint32_t* status, cudaStream_t stream);
+int launch_fa_fwd(const DeviceCtx& ctx, void* O, void* lse, const void* Q, const void* K,
+                  const void* V, int B, int H, int H_kv, int S, int D, float sm_scale, int causal,
+                  unsigned flags, void* dbg, uint32_t* status, cudaStream_t stream);
 int launch_selftest(const DeviceCtx& ctx, int which, void* out_s, void* out_o, const void* q,
                     const void* k, const void* v, const void* p, cudaStream_t stream);
 

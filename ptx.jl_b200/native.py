@@ -61,6 +61,8 @@ def lib() -> ctypes.CDLL:
     L.gemm_bf16.argtypes = [vp, vp, vp, ci, ci, ci, ci, cu, vp]
     L.fa_fwd_bf16.restype = ci
     L.fa_fwd_bf16.argtypes = [vp, vp, vp, vp, ci, ci, ci, ci, cf, ci, cu, vp, vp]
+    L.fa_fwd_bf16_ex.restype = ci
+    L.fa_fwd_bf16_ex.argtypes = [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, cf, ci, cu, vp, vp]
     L.fa_fwd_bf16_noalloc.restype = ci
     L.fa_fwd_bf16_noalloc.argtypes = [vp, vp, vp, vp, ci, ci, ci, ci, cf, ci, cu, vp]
     L.ptxb200_sync_status.restype = ci

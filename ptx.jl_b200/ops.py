@@ -36,8 +36,10 @@ def _require_cuda(*tensors: torch.Tensor) -> None:
 def fa_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: bool = False,
            sm_scale: Optional[float] = None, out: Optional[torch.Tensor] = None,
            flags: int = 0, dbg: Optional[torch.Tensor] = None,
-           stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
-    """O = softmax(Q K^T * sm_scale [+causal]) V for [B,H,S,D] bf16 tensors.
+           stream: Optional[torch.cuda.Stream] = None, lse: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """O = softmax(Q K^T * sm_scale [+causal]) V for [B,H,S,D] bf16 tensors
+    (K, V may have fewer heads, H_kv dividing H; `lse` optionally receives the
+    per-row log-sum-exp).
 
     Same operand layout as the reference's fab_setup (bench/flash_attention.jl:41-85):
     [B,H,S,D] row-major == a (B*H*S, D) matrix with D contiguous.
@@ -45,9 +47,15 @@ def fa_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: bool = 
     _require_cuda(q, k, v)
     if q.dtype != torch.bfloat16 or k.dtype != torch.bfloat16 or v.dtype != torch.bfloat16:
         raise ValueError("fa_fwd takes bf16 tensors")
-    if q.dim() != 4 or q.shape != k.shape or q.shape != v.shape:
-        raise ValueError("fa_fwd takes three [B,H,S,D] tensors of equal shape")
+    if q.dim() != 4 or k.shape != v.shape or k.dim() != 4 or (q.shape[0], q.shape[2], q.shape[3]) != (
+            k.shape[0], k.shape[2], k.shape[3]):
+        raise ValueError("fa_fwd takes Q [B,H,S,D] and K, V [B,H_kv,S,D]")
     B, H, S, D = q.shape
+    H_kv = k.shape[1]
+    if lse is not None:
+        _require_cuda(lse)
+        if lse.dtype != torch.float32 or lse.numel() != B * H * S:
+            raise ValueError("lse must be B*H*S float32")
     if sm_scale is None:
         sm_scale = 1.0 / math.sqrt(D)
     if out is None:
@@ -56,9 +64,9 @@ def fa_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: bool = 
         _require_cuda(out)
         if out.shape != q.shape or out.dtype != torch.bfloat16:
             raise ValueError("out must match q")
-    rc = native.lib().fa_fwd_bf16(_ptr(out), _ptr(q), _ptr(k), _ptr(v), B, H, S, D,
-                                  ctypes.c_float(sm_scale), int(bool(causal)), flags, _ptr(dbg),
-                                  _stream(stream))
+    rc = native.lib().fa_fwd_bf16_ex(_ptr(out), _ptr(lse), _ptr(q), _ptr(k), _ptr(v), B, H, H_kv, S, D,
+                                     ctypes.c_float(sm_scale), int(bool(causal)), flags, _ptr(dbg),
+                                     _stream(stream))
     native.check(rc)
     return out
 

@@ -90,6 +90,36 @@ def test_full_size_properties(pkg, gpu, causal):
         assert torch.equal(o1[:, :, 0, :], v[:, :, 0, :])
 
 
+@pytest.mark.parametrize("D,causal,H,H_kv", [(128, False, 8, 2), (128, True, 6, 3), (64, False, 4, 1), (64, True, 8, 8)])
+def test_grouped_heads_and_lse(pkg, gpu, oracle_mod, D, causal, H, H_kv):
+    """fa_fwd_bf16_ex: query head h attends to key/value head h / (H / H_kv), and the
+    per-row log-sum-exp comes out next to O. O is checked against the oracle on K/V
+    repeated per group; LSE against float64 (tolerance: fp32 statistics of bf16 data)."""
+    B, S = 2, 512
+    g = torch.Generator().manual_seed(4100 + D + H)
+    q = torch.randn(B, H, S, D, generator=g).to(torch.bfloat16)
+    k = torch.randn(B, H_kv, S, D, generator=g).to(torch.bfloat16)
+    v = torch.randn(B, H_kv, S, D, generator=g).to(torch.bfloat16)
+    lse = torch.full((B, H, S), float("nan"), dtype=torch.float32, device=gpu)
+    o = pkg.ops.fa_fwd(q.to(gpu), k.to(gpu), v.to(gpu), causal=causal, lse=lse)
+    assert pkg.ops.sync_status() == 0
+    ke = k.repeat_interleave(H // H_kv, dim=1)
+    ve = v.repeat_interleave(H // H_kv, dim=1)
+    ref = oracle_mod.attention_ref_c(bits(q).reshape(B * H, S, D), bits(ke).reshape(B * H, S, D),
+                                     bits(ve).reshape(B * H, S, D), 1.0 / D ** 0.5, causal)
+    mx, mean = attn_errors(o, ref)
+    assert mx <= ATTN_MAX_ABS and mean <= ATTN_MEAN_ABS, (mx, mean)
+    got = lse.cpu().numpy().reshape(B * H, S)
+    qf, kf = q.float().numpy().reshape(B * H, S, D), ke.float().numpy().reshape(B * H, S, D)
+    for i in (0, B * H // 2, B * H - 1):
+        want = oracle_mod.attention_lse_numpy(qf[i], kf[i], 1.0 / D ** 0.5, causal)
+        np.testing.assert_allclose(got[i], want, rtol=0, atol=2e-3)
+    L = pkg.native.lib()
+    P = o.data_ptr()
+    import ctypes
+    assert L.fa_fwd_bf16_ex(P, None, P, P, P, 1, 6, 4, 256, 128, ctypes.c_float(0.1), 0, 0, None, None) == pkg.native.E_SHAPE
+
+
 def test_rejects_bad_arguments(pkg, gpu):
     L = pkg.native.lib()
     t = torch.zeros(1, 1, 256, 128, dtype=torch.bfloat16, device=gpu)
