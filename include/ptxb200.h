@@ -84,7 +84,8 @@ int gemm_bf16(void* C, const void* A, const void* Bt, int M, int N, int K, int l
  *   Q, K, V, O  [B,H,S,D] row-major bf16 == a 2-D (B*H*S, D) matrix, D contiguous
  *               (the reference's layout: flash_attention_defs.jl:90, 979-986)
  *   D           64 or 128
- *   S           multiple of 256
+ *   S           multiple of 128 (work is cut in 256-row items; an odd number of
+ *               128-row blocks leaves the last item of each head half empty)
  *   causal      0: every key; 1: key j is kept for query i iff j <= i
  *               (mask convention of test/gpu/ampere/flash_attention.jl:176-186)
  *   dbg         NULL, or 64 uint32 words on the device that receive per-role

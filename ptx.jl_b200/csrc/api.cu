@@ -169,7 +169,7 @@ int fa_fwd_bf16_ex(void* O, void* lse, const void* Q, const void* K, const void*
   if (causal != 0 && causal != 1) return PTXB200_E_INVALID;
   if (flags & ~PTXB200_FA_NO_LAZY_RESCALE) return PTXB200_E_INVALID;
   if (!(sm_scale > 0.0f) || !(sm_scale < 1e30f)) return PTXB200_E_INVALID;
-  if ((D != 64 && D != 128) || S % 256 != 0 || H % H_kv != 0) return PTXB200_E_SHAPE;
+  if ((D != 64 && D != 128) || S % 128 != 0 || H % H_kv != 0) return PTXB200_E_SHAPE;
   if ((long long)B * H * S >= (1ll << 31)) return PTXB200_E_SHAPE;
   if (!aligned16(O) || !aligned16(Q) || !aligned16(K) || !aligned16(V)) return PTXB200_E_ALIGN;
   if ((dbg != nullptr && !aligned16(dbg)) || (lse != nullptr && !aligned16(lse))) return PTXB200_E_ALIGN;

@@ -147,7 +147,7 @@ struct FaCfg {
 struct FaParams {
   __nv_bfloat16* o;
   int seqlen;        // S
-  int num_mblocks;   // S / 256
+  int num_mblocks;   // ceil(S / 256)
   int bh;            // B * H
   int total_work;    // num_mblocks * bh
   float scale_log2;  // sm_scale * log2(e)
@@ -181,8 +181,9 @@ __device__ __forceinline__ void decode_item(const FaParams& p, int w, int& mb, i
 template <bool kCausal>
 __device__ __forceinline__ void tile_counts(const FaParams& p, int mb, int& nt0, int& nt1) {
   if (kCausal) {
-    nt0 = 2 * mb + 1;
-    nt1 = 2 * mb + 2;
+    const int nt_all = p.seqlen / kAttnRows;
+    nt0 = min(2 * mb + 1, nt_all);
+    nt1 = min(2 * mb + 2, nt_all);   // equals nt0 in a last block that has only its first stage
   } else {
     nt0 = nt1 = p.seqlen / kAttnRows;
   }
@@ -613,10 +614,13 @@ FA_MMA_UNROLL
         tc_fence_after();
         const float l_total = stats_l[s * 128 + row] + l_part[s];
         const float inv_l = 1.0f / l_total;
-        if (p.lse != nullptr) {
+        if (p.lse != nullptr && mb * 2 * kAttnRows + s * kAttnRows < p.seqlen) {
           // sum_j 2^(s_j c) = 2^(m c) * l with basis -m c in neg_prev: natural log of it
           p.lse[q_row0 + s * kAttnRows + row] = (log2f(l_total) - neg_prev[s]) * 0.6931471805599453f;
         }
+        // a sequence of an odd number of 128-row blocks ends with a half-empty item: its
+        // second stage computes on rows past the end and is simply not written out
+        const bool stage_valid = mb * 2 * kAttnRows + s * kAttnRows < p.seqlen;
         __nv_bfloat16* dst = p.o + (size_t)(q_row0 + s * kAttnRows + row) * D;
 #pragma unroll 1
         for (int c = 0; c < D / 32; ++c) {
@@ -634,7 +638,7 @@ FA_MMA_UNROLL
             const uint32_t p1 = pack_bf16x2(__uint_as_float(o[8 * i + 2]) * inv_l, __uint_as_float(o[8 * i + 3]) * inv_l);
             const uint32_t p2 = pack_bf16x2(__uint_as_float(o[8 * i + 4]) * inv_l, __uint_as_float(o[8 * i + 5]) * inv_l);
             const uint32_t p3 = pack_bf16x2(__uint_as_float(o[8 * i + 6]) * inv_l, __uint_as_float(o[8 * i + 7]) * inv_l);
-            st_global_v4(dst + c * 32 + 8 * i, p0, p1, p2, p3);
+            if (stage_valid) st_global_v4(dst + c * 32 + 8 * i, p0, p1, p2, p3);
           }
         }
       }
@@ -689,7 +693,7 @@ int launch_fa_fwd(const DeviceCtx& ctx, void* O, void* lse, const void* Q, const
   FaParams p;
   p.o = reinterpret_cast<__nv_bfloat16*>(O);
   p.seqlen = S;
-  p.num_mblocks = S / 256;
+  p.num_mblocks = (S + 255) / 256;
   p.bh = B * H;
   p.total_work = p.num_mblocks * p.bh;
   p.scale_log2 = sm_scale * 1.4426950408889634f;
@@ -781,7 +785,7 @@ extern "C" int fa_fwd_bf16_noalloc(void* O, const void* Q, const void* K, const 
   if (causal != 0 && causal != 1) return PTXB200_E_INVALID;
   if (flags & ~PTXB200_FA_NO_LAZY_RESCALE) return PTXB200_E_INVALID;
   if (!(sm_scale > 0.0f) || !(sm_scale < 1e30f)) return PTXB200_E_INVALID;
-  if ((D != 64 && D != 128) || S % 256 != 0) return PTXB200_E_SHAPE;
+  if ((D != 64 && D != 128) || S % 128 != 0) return PTXB200_E_SHAPE;
   if ((long long)B * H * S >= (1ll << 31)) return PTXB200_E_SHAPE;
   if (!aligned16(O) || !aligned16(Q) || !aligned16(K) || !aligned16(V)) return PTXB200_E_ALIGN;
   cudaStream_t stream = (cudaStream_t)stream_v;
@@ -823,7 +827,7 @@ extern "C" int fa_fwd_bf16_noalloc(void* O, const void* Q, const void* K, const 
   FaParams p;
   p.o = reinterpret_cast<__nv_bfloat16*>(O);
   p.seqlen = S;
-  p.num_mblocks = S / 256;
+  p.num_mblocks = (S + 255) / 256;
   p.bh = B * H;
   p.total_work = p.num_mblocks * p.bh;
   p.scale_log2 = sm_scale * 1.4426950408889634f;

@@ -53,6 +53,24 @@ def test_many_items_per_cta(pkg, gpu, oracle_mod, D, causal):
     assert mx <= ATTN_MAX_ABS and mean <= ATTN_MEAN_ABS, (mx, mean)
 
 
+@pytest.mark.parametrize("S", [128, 384, 640])
+@pytest.mark.parametrize("D,causal", [(128, False), (128, True), (64, True)])
+def test_odd_number_of_128_row_blocks(pkg, gpu, oracle_mod, S, D, causal):
+    """S a multiple of 128 but not of 256 (the reference asserts these away,
+    bench/flash_attention.jl:43-47): the last work item of every head has only its
+    first stage, whose second stage lies over the next head's first rows: a stray
+    write there would corrupt that head's output and show up here."""
+    B, H = 2, 3
+    q, k, v = seeded_qkv(B, H, S, D, 900 + S, 1.0)
+    o = torch.full((B, H, S, D), 7.0, dtype=torch.bfloat16, device=gpu)
+    pkg.ops.fa_fwd(q.to(gpu), k.to(gpu), v.to(gpu), causal=causal, out=o)
+    assert pkg.ops.sync_status() == 0
+    ref = oracle_mod.attention_ref_c(bits(q).reshape(B * H, S, D), bits(k).reshape(B * H, S, D),
+                                     bits(v).reshape(B * H, S, D), 1.0 / D ** 0.5, causal)
+    mx, mean = attn_errors(o, ref)
+    assert mx <= ATTN_MAX_ABS and mean <= ATTN_MEAN_ABS, (mx, mean)
+
+
 def test_baseline_config_1_shape(pkg, gpu, oracle_mod):
     """B=1 H=4 S=256 D=64 non-causal, N(0,1) inputs: the CPU-runnable baseline case."""
     mx, mean = _run(pkg, gpu, oracle_mod, 1, 4, 256, 64, False, sigma_qk=1.0, seed=20260001)
