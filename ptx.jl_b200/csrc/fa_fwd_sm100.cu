@@ -189,6 +189,141 @@ __device__ __forceinline__ void tile_counts(const FaParams& p, int mb, int& nt0,
   }
 }
 
+// The MMA-issue thread (one lane of warp 12).
+//
+// Its instruction stream is what paces the tensor pipe: with the ring slot changing
+// every tile, forming the slot's descriptors costs this one thread about 320 clk per
+// tile pair on top of 2050 clk of tensor time (measured in isolation). Two ways
+// around that were built and measured no better in the full kernel: one switch per
+// tile over the slot with every descriptor an immediate (faster in isolation, slower
+// here, most of all for causal shapes), and issuing from the converged warp with an
+// elected lane (the GEMM kernel's scheme).
+template <int D, bool kCausal, bool kConv>
+__device__ __forceinline__ void fa_mma_role(const FaParams& p, uint32_t base, uint32_t tmem,
+                                            const WaitCtx& wctx) {
+  using C = FaCfg<D>;
+  using T = AttnTile<D>;
+  constexpr int kSlots = C::kSlots;
+  const uint32_t q_smem = base + C::kOffQ;
+  const uint32_t kv_smem = base + C::kOffKV;
+  const uint32_t bars = base + C::kOffBars;
+  auto bar = [bars](int idx) -> uint32_t { return bars + 8u * (uint32_t)idx; };
+
+  auto wait = [&](uint32_t b, uint32_t parity, uint32_t site) {
+    if (kConv) mbar_wait_warp(b, parity, wctx, site); else mbar_wait(b, parity, wctx, site);
+  };
+  auto commit = [&](uint32_t b) { if (kConv) tc_commit_warp(b); else tc_commit(b); };
+  [[maybe_unused]] const bool stamp_lane = !kConv || (threadIdx.x & 31) == 0;
+
+  uint32_t slot = 0;      // ring slot of the next K/V tile
+  uint32_t ring_ph = 0;   // phase of that slot's kv_full barrier
+  uint32_t item_i = 0;
+  uint32_t cnt_pv[2] = {0, 0};   // P*V products issued per stage (p_full phases)
+  uint32_t kv_count = 0;
+
+  // S_stage = Q_stage K^T with K in ring slot KS.
+  auto qk = [&](int stage, uint32_t KS) {
+    const uint32_t qa = q_smem + stage * T::kTileBytes;
+    const uint32_t ka = kv_smem + KS * T::kTileBytes;
+FA_MMA_UNROLL
+    for (int kk = 0; kk < T::kQKAtoms; ++kk)
+#if defined(PTXB200_FA_ABLATE) && (PTXB200_FA_ABLATE == 5 || PTXB200_FA_ABLATE == 6)
+      if (kk < 0)
+#endif
+      if (kConv)
+        tc_mma_ss_warp(tmem + C::kColS + stage * 128, T::kmajor_lo(qa, kk), T::kKMajorHi,
+                       T::kmajor_lo(ka, kk), T::kKMajorHi, T::kIdescQK, kk != 0 ? 1u : 0u);
+      else
+        tc_mma_ss(tmem + C::kColS + stage * 128, T::kmajor_lo(qa, kk), T::kKMajorHi,
+                  T::kmajor_lo(ka, kk), T::kKMajorHi, T::kIdescQK, kk != 0 ? 1u : 0u);
+    commit(bar(C::kBarSFull + stage));
+  };
+  // O_stage (+)= P_stage V with V in ring slot VS, issued per 64-column half of P as
+  // the softmax publishes it: k16 steps 0-3 run while the second half is still being
+  // exponentiated (the reference's split-P idea, flash_attention_defs.jl:36-50).
+  auto pv = [&](int stage, uint32_t VS, bool accumulate, uint32_t parity) {
+    const uint32_t va = kv_smem + VS * T::kTileBytes;
+FA_MMA_UNROLL
+    for (int h = 0; h < 2; ++h) {
+      wait(bar(C::kBarPFull + 2 * stage + h), parity, kSiteMmaPFull);
+      tc_fence_after();
+FA_MMA_UNROLL
+      for (int kk = 4 * h; kk < 4 * h + 4; ++kk)
+#if defined(PTXB200_FA_ABLATE) && (PTXB200_FA_ABLATE == 4 || PTXB200_FA_ABLATE == 6)
+        if (kk < 0)
+#endif
+        if (kConv)
+          tc_mma_ts_warp(tmem + C::kColO + stage * D, T::p_tmem(tmem, C::kColS + stage * 128, kk),
+                         T::v_lo(va, kk), T::kVHi, T::kIdescPV, (accumulate || kk != 0) ? 1u : 0u);
+        else
+          tc_mma_ts(tmem + C::kColO + stage * D, T::p_tmem(tmem, C::kColS + stage * 128, kk),
+                    T::v_lo(va, kk), T::kVHi, T::kIdescPV, (accumulate || kk != 0) ? 1u : 0u);
+    }
+  };
+  // First tile of an item: K_0 sits in slot KS; S_s = Q_s K_0^T for both stages.
+  auto first = [&](uint32_t KS, uint32_t qph, int nt_max) {
+    wait(bar(C::kBarQFull + 0), qph, kSiteMmaQFull);
+    wait(bar(C::kBarKvFull + KS), ring_ph, kSiteMmaKvFull);
+    tc_fence_after();
+    qk(0, KS);
+    wait(bar(C::kBarQFull + 1), qph, kSiteMmaQFull);
+    tc_fence_after();
+    qk(1, KS);
+    commit(bar(C::kBarKvFree + KS));
+    if (nt_max == 1) commit(bar(C::kBarQFree));
+  };
+  // Key tile j of an item: V_j sits in slot VS and, if there is a next tile, K_{j+1}
+  // in the slot behind it.
+  auto step = [&](uint32_t VS, int j, const int (&nt)[2]) {
+    const uint32_t KS = (VS + 1 == (uint32_t)kSlots) ? 0u : VS + 1;
+    const int nt_max = nt[1];
+    const bool has_next = (j + 1 < nt_max);
+    FA_TSTAMP(stamp_lane && blockIdx.x == 0 && item_i == 0, 2, j, 6);
+    wait(bar(C::kBarKvFull + VS), ring_ph, kSiteMmaKvFull);
+    if (has_next)
+      wait(bar(C::kBarKvFull + KS), KS == 0 ? (ring_ph ^ 1u) : ring_ph, kSiteMmaKvFull);
+    FA_TSTAMP(stamp_lane && blockIdx.x == 0 && item_i == 0, 2, j, 7);
+FA_MMA_UNROLL
+    for (int s = 0; s < 2; ++s) {
+      if (!kCausal || j < nt[s]) {
+        FA_TSTAMP(stamp_lane && blockIdx.x == 0 && item_i == 0, 2, j, 3 * s + 0);
+        pv(s, VS, j > 0, cnt_pv[s] & 1u);
+        ++cnt_pv[s];
+        FA_TSTAMP(stamp_lane && blockIdx.x == 0 && item_i == 0, 2, j, 3 * s + 1);
+        if (j + 1 < nt[s]) qk(s, KS);
+        else commit(bar(C::kBarODone + s));
+        FA_TSTAMP(stamp_lane && blockIdx.x == 0 && item_i == 0, 2, j, 3 * s + 2);
+      }
+    }
+    commit(bar(C::kBarKvFree + VS));
+    if (has_next) commit(bar(C::kBarKvFree + KS));
+    if (j + 2 == nt_max) commit(bar(C::kBarQFree));   // last Q K^T issued
+  };
+  auto advance = [&](uint32_t n) {
+    slot += n;
+    kv_count += n;
+    if (slot >= (uint32_t)kSlots) { slot -= kSlots; ring_ph ^= 1u; }
+  };
+  for (int w = blockIdx.x; w < p.total_work; w += gridDim.x, ++item_i) {
+    int mb, bh, nt[2];
+    decode_item<kCausal>(p, w, mb, bh);
+    tile_counts<kCausal>(p, mb, nt[0], nt[1]);
+    const int nt_max = nt[1];
+    const uint32_t qph = item_i & 1u;
+    first(slot, qph, nt_max);
+    advance(1);
+    for (int j = 0; j < nt_max; ++j) {
+      step(slot, j, nt);
+      advance(j + 1 < nt_max ? 2u : 1u);
+    }
+  }
+  if (p.dbg != nullptr && blockIdx.x == 0 && stamp_lane) {
+    p.dbg[1] = kv_count;
+    p.dbg[2] = cnt_pv[0];
+    p.dbg[3] = cnt_pv[1];
+  }
+}
+
 // kCtaFlags: additionally mark, in p.cta_flags[blockIdx.x], every CTA in which a
 // bounded wait ran out (used by the entry point that keeps its scratch in a static
 // device array).
@@ -298,91 +433,11 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
         if (p.dbg != nullptr && blockIdx.x == 0) p.dbg[0] = kv_it;
       }
     } else if (warp == 12) {
-      if (elect_one()) {
-        uint32_t kv_it = 0, item_i = 0;
-        uint32_t cnt_pv[2] = {0, 0};   // P*V products issued per stage (p_full and o_ready phases)
-        auto kv_wait = [&]() -> uint32_t {   // returns the ring slot
-          const uint32_t s = kv_it % C::kSlots;
-          const uint32_t ph = (kv_it / C::kSlots) & 1u;
-          mbar_wait(bar(C::kBarKvFull + s), ph, wctx, kSiteMmaKvFull);
-          ++kv_it;
-          return s;
-        };
-        auto qk = [&](int stage, uint32_t kslot) {   // S_stage = Q_stage K^T
-          const uint32_t qa = q_smem + stage * T::kTileBytes;
-          const uint32_t ka = kv_smem + kslot * T::kTileBytes;
-FA_MMA_UNROLL
-          for (int kk = 0; kk < T::kQKAtoms; ++kk)
-#if defined(PTXB200_FA_ABLATE) && (PTXB200_FA_ABLATE == 5 || PTXB200_FA_ABLATE == 6)
-            if (kk < 0)
+#ifdef PTXB200_FA_MMA_CONVERGED
+      fa_mma_role<D, kCausal, true>(p, base, tmem, wctx);
+#else
+      if (elect_one()) fa_mma_role<D, kCausal, false>(p, base, tmem, wctx);
 #endif
-            tc_mma_ss(tmem + C::kColS + stage * 128, T::kmajor_lo(qa, kk), T::kKMajorHi,
-                      T::kmajor_lo(ka, kk), T::kKMajorHi, T::kIdescQK, kk != 0 ? 1u : 0u);
-          tc_commit(bar(C::kBarSFull + stage));
-        };
-        // O_stage (+)= P_stage V, issued per 64-column half of P as the softmax
-        // publishes it: k16 steps 0-3 run while the second half is still being
-        // exponentiated (the reference's split-P idea, flash_attention_defs.jl:36-50).
-        auto pv = [&](int stage, uint32_t vslot, bool accumulate, uint32_t parity) {
-          const uint32_t va = kv_smem + vslot * T::kTileBytes;
-FA_MMA_UNROLL
-          for (int h = 0; h < 2; ++h) {
-            mbar_wait(bar(C::kBarPFull + 2 * stage + h), parity, wctx, kSiteMmaPFull);
-            tc_fence_after();
-FA_MMA_UNROLL
-            for (int kk = 4 * h; kk < 4 * h + 4; ++kk)
-#if defined(PTXB200_FA_ABLATE) && (PTXB200_FA_ABLATE == 4 || PTXB200_FA_ABLATE == 6)
-              if (kk < 0)
-#endif
-              tc_mma_ts(tmem + C::kColO + stage * D, T::p_tmem(tmem, C::kColS + stage * 128, kk),
-                        T::v_lo(va, kk), T::kVHi, T::kIdescPV, (accumulate || kk != 0) ? 1u : 0u);
-          }
-        };
-        for (int w = blockIdx.x; w < p.total_work; w += gridDim.x, ++item_i) {
-          int mb, bh, nt[2];
-          decode_item<kCausal>(p, w, mb, bh);
-          tile_counts<kCausal>(p, mb, nt[0], nt[1]);
-          const int nt_max = nt[1];
-          const uint32_t qph = item_i & 1u;
-          mbar_wait(bar(C::kBarQFull + 0), qph, wctx, kSiteMmaQFull);
-          const uint32_t k0 = kv_wait();
-          tc_fence_after();
-          qk(0, k0);
-          mbar_wait(bar(C::kBarQFull + 1), qph, wctx, kSiteMmaQFull);
-          tc_fence_after();
-          qk(1, k0);
-          tc_commit(bar(C::kBarKvFree + k0));
-          if (nt_max == 1) tc_commit(bar(C::kBarQFree));
-          for (int j = 0; j < nt_max; ++j) {
-            FA_TSTAMP(w == 0, 2, j, 6);
-            const uint32_t vslot = kv_wait();
-            const bool has_next = (j + 1 < nt_max);
-            uint32_t kslot = 0;
-            if (has_next) kslot = kv_wait();
-            FA_TSTAMP(w == 0, 2, j, 7);
-FA_MMA_UNROLL
-            for (int s = 0; s < 2; ++s) {
-              if (j < nt[s]) {
-                FA_TSTAMP(w == 0, 2, j, 3 * s + 0);
-                pv(s, vslot, j > 0, cnt_pv[s] & 1u);
-                ++cnt_pv[s];
-                FA_TSTAMP(w == 0, 2, j, 3 * s + 1);
-                if (j + 1 < nt[s]) qk(s, kslot);
-                else tc_commit(bar(C::kBarODone + s));
-                FA_TSTAMP(w == 0, 2, j, 3 * s + 2);
-              }
-            }
-            tc_commit(bar(C::kBarKvFree + vslot));
-            if (has_next) tc_commit(bar(C::kBarKvFree + kslot));
-            if (j + 2 == nt_max) tc_commit(bar(C::kBarQFree));   // last Q K^T issued
-          }
-        }
-        if (p.dbg != nullptr && blockIdx.x == 0) {
-          p.dbg[1] = kv_it;
-          p.dbg[2] = cnt_pv[0];
-          p.dbg[3] = cnt_pv[1];
-        }
-      }
     }
   } else if (warp < 8) {
     // =====================================================================
