@@ -79,6 +79,51 @@ int gemm_bf16(void* C, const void* A, const void* Bt, int M, int N, int K, int l
               unsigned flags, void* stream);
 
 /*
+ * Uniform grouped GEMM: C[g] = A[g] * B[g] for g in [0, G), every group of the
+ * same shape, in one launch.
+ *
+ *   A   [G*M, K] row-major bf16: group g is rows g*M .. g*M+M-1
+ *   Bt  [G*N, K] row-major bf16: group g's B transposed is rows g*N .. g*N+N-1
+ *   C   [G*M, N] row-major with leading dimension ldc (elements), ldc >= N
+ *
+ * Shape contract: G > 0, M % 128 == 0, N % 64 == 0, K % 64 == 0;
+ * ldc * sizeof(element) % 16 == 0. Flags as gemm_bf16.
+ *
+ * Replaces the reference's _run_ggb launch of _grouped_gemm_bw_kernel!
+ * (test/gpu/blackwell/grouped_gemm.jl:43-158, 208-232): same stacked operand
+ * packing (_ggb_pack_A / _ggb_pack_B, :185-206), grid-z = group there, one more
+ * factor of the persistent tile loop here; the reference writes fp32 only and fixes
+ * N = 64.
+ */
+int gemm_bf16_grouped(void* C, const void* A, const void* Bt, int G, int M, int N, int K, int ldc,
+                      unsigned flags, void* stream);
+
+/*
+ * Row-wise fp32 kernels either side of attention in a transformer block. X and Y
+ * are [rows, N] row-major fp32, W and Bias are [N] fp32; one read of X and one
+ * write of Y per call. Shape contract: rows > 0, N % 4 == 0, 4 <= N <= 32768;
+ * every pointer 16-byte aligned (so every row is). Asynchronous on `stream`.
+ *
+ *   softmax_f32     Y[r,i] = exp(X[r,i] - max_i X[r,:]) / sum_i exp(X[r,i] - max)
+ *                   replaces _softmax_v4_kernel! (test/gpu/softmax.jl:30-140)
+ *   rms_norm_f32    Y[r,i] = X[r,i] * W[i] / sqrt(mean_i X[r,:]^2 + eps)
+ *                   replaces _rms_norm_v4_kernel! (test/gpu/rms_norm.jl:30-106)
+ *   layer_norm_f32  Y[r,i] = (X[r,i] - mean) / sqrt(var + eps) * W[i] + Bias[i]
+ *                   (biased variance) replaces _layer_norm_v4_kernel!
+ *                   (test/gpu/layer_norm.jl:24-122)
+ *   swiglu_f32      out[k] = gate[k] / (1 + exp(-gate[k])) * up[k] over n elements,
+ *                   n % 4 == 0; replaces _swiglu_v4_kernel! (test/gpu/swiglu.jl:31-69)
+ *
+ * The reference kernels take N (or F) and the block size as compile-time values
+ * with N % (block*4) == 0 and launch one CTA per row; these take them at run time.
+ */
+int softmax_f32(void* Y, const void* X, int rows, int N, void* stream);
+int rms_norm_f32(void* Y, const void* X, const void* W, int rows, int N, float eps, void* stream);
+int layer_norm_f32(void* Y, const void* X, const void* W, const void* Bias, int rows, int N,
+                   float eps, void* stream);
+int swiglu_f32(void* out, const void* gate, const void* up, long long n, void* stream);
+
+/*
  * O = softmax(Q K^T * sm_scale [+ causal mask]) V, row-wise, per (batch, head).
  *
  *   Q, K, V, O  [B,H,S,D] row-major bf16 == a 2-D (B*H*S, D) matrix, D contiguous

@@ -76,6 +76,41 @@ def gemm_ref_numpy(A: np.ndarray, B: np.ndarray) -> np.ndarray:
     return (_quantise(A) @ _quantise(B)).astype(np.float32)
 
 
+# ----------------------------- row-wise neighbours ------------------------------
+# Restatements of the reference's CPU references for its row-wise kernels, float64
+# inside like theirs. Parity unpinned in the same sense as the attention oracle:
+# the reference's tests hold tolerances (atol 1e-4, rtol 1e-3), not output vectors.
+
+def softmax_ref_numpy(X: np.ndarray) -> np.ndarray:
+    """softmax_ref, test/gpu/softmax.jl:139-149."""
+    x = X.astype(np.float64)
+    x = x - x.max(axis=1, keepdims=True)
+    e = np.exp(x)
+    return (e / e.sum(axis=1, keepdims=True)).astype(np.float32)
+
+
+def rms_norm_ref_numpy(X: np.ndarray, W: np.ndarray, eps: float) -> np.ndarray:
+    """rms_norm_ref, test/gpu/rms_norm.jl:109-119."""
+    x = X.astype(np.float64)
+    ms = (x * x).sum(axis=1, keepdims=True) / x.shape[1]
+    return (x * (1.0 / np.sqrt(ms + np.float64(np.float32(eps)))) * W.astype(np.float64)).astype(np.float32)
+
+
+def layer_norm_ref_numpy(X: np.ndarray, W: np.ndarray, B: np.ndarray, eps: float) -> np.ndarray:
+    """layer_norm_ref, test/gpu/layer_norm.jl:125-136 (biased variance)."""
+    x = X.astype(np.float64)
+    m = x.sum(axis=1, keepdims=True) / x.shape[1]
+    v = ((x - m) ** 2).sum(axis=1, keepdims=True) / x.shape[1]
+    return ((x - m) * (1.0 / np.sqrt(v + np.float64(np.float32(eps)))) * W.astype(np.float64)
+            + B.astype(np.float64)).astype(np.float32)
+
+
+def swiglu_ref_numpy(gate: np.ndarray, up: np.ndarray) -> np.ndarray:
+    """swiglu_ref, test/gpu/swiglu.jl:70-75."""
+    g = gate.astype(np.float64)
+    return (g * (1.0 / (1.0 + np.exp(-g))) * up.astype(np.float64)).astype(np.float32)
+
+
 # ----------------------------- C restatement -----------------------------------
 
 def build_c_oracle(force: bool = False) -> str:

@@ -15,7 +15,7 @@ __all__ = ["native", "build"]
 
 def __getattr__(name):
     # torch-dependent modules load lazily so that build/symbol checks stay light
-    if name in ("ops", "flash_attention", "gemm_highperf", "build", "sharding"):
+    if name in ("ops", "flash_attention", "gemm_highperf", "rowwise", "build", "sharding"):
         import importlib
         return importlib.import_module(f"{__name__}.{name}")
     raise AttributeError(name)

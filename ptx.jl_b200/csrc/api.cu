@@ -158,7 +158,67 @@ int gemm_bf16(void* C, const void* A, const void* Bt, int M, int N, int K, int l
   DeviceCtx* ctx = nullptr;
   int rc = current_ctx(&ctx);
   if (rc != PTXB200_OK) return rc;
-  return launch_gemm(*ctx, C, A, Bt, M, N, K, ldc, flags, (cudaStream_t)stream);
+  return launch_gemm(*ctx, C, A, Bt, 1, M, N, K, ldc, flags, (cudaStream_t)stream);
+}
+
+int gemm_bf16_grouped(void* C, const void* A, const void* Bt, int G, int M, int N, int K, int ldc,
+                      unsigned flags, void* stream) {
+  if (C == nullptr || A == nullptr || Bt == nullptr) return PTXB200_E_INVALID;
+  if (G <= 0 || M <= 0 || N <= 0 || K <= 0 || ldc < N) return PTXB200_E_INVALID;
+  if (flags & ~PTXB200_GEMM_F32_OUT) return PTXB200_E_INVALID;
+  if (M % 128 != 0 || N % 64 != 0 || K % 64 != 0) return PTXB200_E_SHAPE;
+  if ((long long)G * M >= (1ll << 31) || (long long)G * N >= (1ll << 31)) return PTXB200_E_SHAPE;
+  const size_t esz = (flags & PTXB200_GEMM_F32_OUT) ? 4 : 2;
+  if (!aligned16(C) || !aligned16(A) || !aligned16(Bt) || ((size_t)ldc * esz) % 16 != 0)
+    return PTXB200_E_ALIGN;
+  DeviceCtx* ctx = nullptr;
+  int rc = current_ctx(&ctx);
+  if (rc != PTXB200_OK) return rc;
+  return launch_gemm(*ctx, C, A, Bt, G, M, N, K, ldc, flags, (cudaStream_t)stream);
+}
+
+namespace {
+int rowwise_entry(int op, void* y, const void* x, const void* w, const void* bias, int rows, int n,
+                  float eps, void* stream) {
+  if (y == nullptr || x == nullptr || (op >= 1 && w == nullptr) || (op == 2 && bias == nullptr))
+    return PTXB200_E_INVALID;
+  if (rows <= 0 || n <= 0) return PTXB200_E_INVALID;
+  if (op >= 1 && !(eps >= 0.0f)) return PTXB200_E_INVALID;
+  if (n % 4 != 0 || n > 32768) return PTXB200_E_SHAPE;
+  if (!aligned16(y) || !aligned16(x) || (w != nullptr && !aligned16(w)) ||
+      (bias != nullptr && !aligned16(bias)))
+    return PTXB200_E_ALIGN;
+  DeviceCtx* ctx = nullptr;
+  int rc = current_ctx(&ctx);
+  if (rc != PTXB200_OK) return rc;
+  return launch_rowwise(*ctx, op, (float*)y, (const float*)x, (const float*)w, (const float*)bias,
+                        rows, n, eps, (cudaStream_t)stream);
+}
+}  // namespace
+
+int softmax_f32(void* Y, const void* X, int rows, int N, void* stream) {
+  return rowwise_entry(0, Y, X, nullptr, nullptr, rows, N, 0.0f, stream);
+}
+
+int rms_norm_f32(void* Y, const void* X, const void* W, int rows, int N, float eps, void* stream) {
+  return rowwise_entry(1, Y, X, W, nullptr, rows, N, eps, stream);
+}
+
+int layer_norm_f32(void* Y, const void* X, const void* W, const void* Bias, int rows, int N,
+                   float eps, void* stream) {
+  return rowwise_entry(2, Y, X, W, Bias, rows, N, eps, stream);
+}
+
+int swiglu_f32(void* out, const void* gate, const void* up, long long n, void* stream) {
+  if (out == nullptr || gate == nullptr || up == nullptr) return PTXB200_E_INVALID;
+  if (n <= 0) return PTXB200_E_INVALID;
+  if (n % 4 != 0) return PTXB200_E_SHAPE;
+  if (!aligned16(out) || !aligned16(gate) || !aligned16(up)) return PTXB200_E_ALIGN;
+  DeviceCtx* ctx = nullptr;
+  int rc = current_ctx(&ctx);
+  if (rc != PTXB200_OK) return rc;
+  return launch_swiglu(*ctx, (float*)out, (const float*)gate, (const float*)up, (size_t)n,
+                       (cudaStream_t)stream);
 }
 
 int fa_fwd_bf16_ex(void* O, void* lse, const void* Q, const void* K, const void* V, int B, int H,

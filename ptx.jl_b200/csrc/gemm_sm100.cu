@@ -19,8 +19,17 @@
 // (bands of kGroupM row-tiles, column-tiles inside a band) so that the ~148
 // tiles in flight share A row panels and B column panels in the 126 MB L2.
 //
-// Algorithmic work per launch: 2*M*N*K flop; compulsory bytes (M*K + N*K)*2 +
-// M*N*sizeof(out).
+// Uniform grouped GEMM (the reference's grid-z = group kernel,
+// test/gpu/blackwell/grouped_gemm.jl:43-158): G problems of one shape with A stacked
+// as [G*M, K], B^T as [G*N, K] and C as [G*M, N] are one more factor of the same
+// persistent tile loop -- tile -> (group, row-tile, column-tile), the group folded
+// into the TMA row coordinates -- so small groups fill the machine together instead
+// of one launch (or one grid-z slice) each. A B^T box that runs past its group's N
+// rows brings in the next group's rows (or zero fill past the end); those columns
+// are computed and never stored.
+//
+// Algorithmic work per launch: 2*G*M*N*K flop; compulsory bytes G*((M*K + N*K)*2 +
+// M*N*sizeof(out)).
 #include "host_common.h"
 #include "sm100_prims.cuh"
 
@@ -65,7 +74,8 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
 template <bool kF32Out>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-            void* __restrict__ c_out, int M, int N, int K, int ldc, uint32_t* status) {
+            void* __restrict__ c_out, int M, int N, int K, int ldc, int groups,
+            uint32_t* status) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (base - smem_u32(smem_raw));
@@ -106,7 +116,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 
   const int tiles_m = M / kBM;
   const int tiles_n = (N + kBN - 1) / kBN;
-  const int total_tiles = tiles_m * tiles_n;
+  const int tiles_per_group = tiles_m * tiles_n;
+  const int total_tiles = tiles_per_group * groups;
   const int kiters = K / kBK;
 
   if (warp == 0) {
@@ -117,14 +128,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       uint32_t it = 0;
       for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
         int tm, tn;
-        tile_coords(tile, tiles_m, tiles_n, tm, tn);
+        const int g = tile / tiles_per_group;
+        tile_coords(tile - g * tiles_per_group, tiles_m, tiles_n, tm, tn);
+        const int a_row = g * M + tm * kBM;
+        const int b_row = g * N + tn * kBN;
         for (int k = 0; k < kiters; ++k, ++it) {
           const uint32_t s = it % kStages;
           const uint32_t ph = (it / kStages) & 1u;
           mbar_wait(bar_empty + 8 * s, ph ^ 1u, wctx, kSiteEmpty);
           mbar_arrive_expect_tx(bar_full + 8 * s, kStageBytes);
-          tma_load_2d(a_base + s * kAStageBytes, &tmap_a, k * kBK, tm * kBM, bar_full + 8 * s);
-          tma_load_2d(b_base + s * kBStageBytes, &tmap_b, k * kBK, tn * kBN, bar_full + 8 * s);
+          tma_load_2d(a_base + s * kAStageBytes, &tmap_a, k * kBK, a_row, bar_full + 8 * s);
+          tma_load_2d(b_base + s * kBStageBytes, &tmap_b, k * kBK, b_row, bar_full + 8 * s);
         }
       }
     }
@@ -166,12 +180,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     uint32_t t = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++t) {
       int tm, tn;
-      tile_coords(tile, tiles_m, tiles_n, tm, tn);
+      const int g = tile / tiles_per_group;
+      tile_coords(tile - g * tiles_per_group, tiles_m, tiles_n, tm, tn);
       const uint32_t buf = t & 1u;
       const uint32_t aph = (t >> 1) & 1u;
       mbar_wait(bar_acc_full + 8 * buf, aph, wctx, kSiteAccFull);
       tc_fence_after();
-      const size_t row = (size_t)tm * kBM + row_in_tile;
+      const size_t row = (size_t)g * M + (size_t)tm * kBM + row_in_tile;
       const int col0 = tn * kBN;
       const uint32_t t_row = tmem_addr(tmem, quad * 32, buf * kAccCols);
 #pragma unroll 1
@@ -215,15 +230,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 
 }  // namespace
 
-int launch_gemm(const DeviceCtx& ctx, void* C, const void* A, const void* Bt, int M, int N, int K,
-                int ldc, unsigned flags, cudaStream_t stream) {
+int launch_gemm(const DeviceCtx& ctx, void* C, const void* A, const void* Bt, int groups, int M, int N,
+                int K, int ldc, unsigned flags, cudaStream_t stream) {
   CUtensorMap ta, tb;
-  int rc = encode_tmap_bf16_2d(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)K * 2, kBM, kBK);
+  int rc = encode_tmap_bf16_2d(&ta, A, (uint64_t)groups * M, (uint64_t)K, (uint64_t)K * 2, kBM, kBK);
   if (rc != PTXB200_OK) return rc;
-  rc = encode_tmap_bf16_2d(&tb, Bt, (uint64_t)N, (uint64_t)K, (uint64_t)K * 2, kBN, kBK);
+  rc = encode_tmap_bf16_2d(&tb, Bt, (uint64_t)groups * N, (uint64_t)K, (uint64_t)K * 2, kBN, kBK);
   if (rc != PTXB200_OK) return rc;
 
-  const int tiles = (M / kBM) * ((N + kBN - 1) / kBN);
+  const int tiles = groups * (M / kBM) * ((N + kBN - 1) / kBN);
   const int grid = tiles < ctx.sm_count ? tiles : ctx.sm_count;
   uint32_t* status = ctx.workspace + kWsStatus;
   if (flags & PTXB200_GEMM_F32_OUT) {
@@ -233,7 +248,7 @@ int launch_gemm(const DeviceCtx& ctx, void* C, const void* A, const void* Bt, in
                                             cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
       attr_done_f32[ctx.device & 63] = true;
     }
-    gemm_kernel<true><<<grid, kThreads, kSmemBytes, stream>>>(ta, tb, C, M, N, K, ldc, status);
+    gemm_kernel<true><<<grid, kThreads, kSmemBytes, stream>>>(ta, tb, C, M, N, K, ldc, groups, status);
   } else {
     static bool attr_done_bf16[64] = {false};
     if (!attr_done_bf16[ctx.device & 63]) {
@@ -241,7 +256,7 @@ int launch_gemm(const DeviceCtx& ctx, void* C, const void* A, const void* Bt, in
                                             cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
       attr_done_bf16[ctx.device & 63] = true;
     }
-    gemm_kernel<false><<<grid, kThreads, kSmemBytes, stream>>>(ta, tb, C, M, N, K, ldc, status);
+    gemm_kernel<false><<<grid, kThreads, kSmemBytes, stream>>>(ta, tb, C, M, N, K, ldc, groups, status);
   }
   PTXB200_CUDA_TRY(cudaGetLastError());
   return PTXB200_OK;

@@ -57,11 +57,16 @@ int encode_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t rows, uint6
   } while (0)
 
 // Kernel launchers (one per .cu file).
-int launch_gemm(const DeviceCtx& ctx, void* C, const void* A, const void* Bt, int M, int N, int K,
-                int ldc, unsigned flags, cudaStream_t stream);
+int launch_gemm(const DeviceCtx& ctx, void* C, const void* A, const void* Bt, int groups, int M, int N,
+                int K, int ldc, unsigned flags, cudaStream_t stream);
 int launch_fa_fwd(const DeviceCtx& ctx, void* O, void* lse, const void* Q, const void* K,
                   const void* V, int B, int H, int H_kv, int S, int D, float sm_scale, int causal,
                   unsigned flags, void* dbg, uint32_t* status, cudaStream_t stream);
+// Row-wise fp32 kernels; op: 0 softmax, 1 RMS norm, 2 layer norm.
+int launch_rowwise(const DeviceCtx& ctx, int op, float* y, const float* x, const float* w,
+                   const float* bias, int rows, int n, float eps, cudaStream_t stream);
+int launch_swiglu(const DeviceCtx& ctx, float* out, const float* gate, const float* up, size_t n,
+                  cudaStream_t stream);
 int launch_selftest(const DeviceCtx& ctx, int which, void* out_s, void* out_o, const void* q,
                     const void* k, const void* v, const void* p, cudaStream_t stream);
 

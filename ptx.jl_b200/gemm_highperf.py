@@ -40,5 +40,29 @@ def run_ghb(M: int, N: int, K: int, *, f32_out: bool = True, device=None):
     return D_d.float().cpu(), A, B
 
 
+def ggb_inputs(G: int, M: int, N: int, K: int, *, scale: float = 0.1) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Host fp32 A3 (G,M,K) and B3 (G,K,N), seed formula of the reference's grouped
+    driver (test/gpu/blackwell/grouped_gemm.jl:210-212)."""
+    gen = torch.Generator().manual_seed(G * 1009 + M * 997 + N * 17 + K)
+    A3 = torch.randn(G, M, K, generator=gen) * scale
+    B3 = torch.randn(G, K, N, generator=gen) * scale
+    return A3, B3
+
+
+def run_ggb(G: int, M: int, N: int, K: int, *, f32_out: bool = True, device=None):
+    """Uniform grouped GEMM, the reference's `_run_ggb` (grouped_gemm.jl:208-232):
+    returns (C_got on host as fp32 (G,M,N), A3, B3). Raises on a device-side timeout."""
+    device = device or torch.device("cuda", torch.cuda.current_device())
+    A3, B3 = ggb_inputs(G, M, N, K)
+    A_d = A3.to(torch.bfloat16).to(device).contiguous()                    # _ggb_pack_A: (G*M, K) K-fast
+    Bt_d = B3.transpose(1, 2).contiguous().to(torch.bfloat16).to(device)   # _ggb_pack_B: (G*N, K) K-fast
+    C_d = ops.gemm_grouped(A_d, Bt_d, f32_out=f32_out)
+    status = ops.sync_status()
+    if status != 0:
+        from . import native
+        raise native.PtxB200Error(status, native.strerror(status))
+    return C_d.float().cpu(), A3, B3
+
+
 def ghb_flops(M: int, N: int, K: int) -> float:
     return 2.0 * M * N * K

@@ -59,6 +59,16 @@ def lib() -> ctypes.CDLL:
     L.ptxb200_last_cuda_error.argtypes = []
     L.gemm_bf16.restype = ci
     L.gemm_bf16.argtypes = [vp, vp, vp, ci, ci, ci, ci, cu, vp]
+    L.softmax_f32.restype = ci
+    L.softmax_f32.argtypes = [vp, vp, ci, ci, vp]
+    L.rms_norm_f32.restype = ci
+    L.rms_norm_f32.argtypes = [vp, vp, vp, ci, ci, ctypes.c_float, vp]
+    L.layer_norm_f32.restype = ci
+    L.layer_norm_f32.argtypes = [vp, vp, vp, vp, ci, ci, ctypes.c_float, vp]
+    L.swiglu_f32.restype = ci
+    L.swiglu_f32.argtypes = [vp, vp, vp, ctypes.c_longlong, vp]
+    L.gemm_bf16_grouped.restype = ci
+    L.gemm_bf16_grouped.argtypes = [vp, vp, vp, ci, ci, ci, ci, ci, cu, vp]
     L.fa_fwd_bf16.restype = ci
     L.fa_fwd_bf16.argtypes = [vp, vp, vp, vp, ci, ci, ci, ci, cf, ci, cu, vp, vp]
     L.fa_fwd_bf16_ex.restype = ci

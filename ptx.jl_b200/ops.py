@@ -96,6 +96,81 @@ def gemm(a: torch.Tensor, bt: torch.Tensor, *, out: Optional[torch.Tensor] = Non
     return out
 
 
+def gemm_grouped(a: torch.Tensor, bt: torch.Tensor, *, out: Optional[torch.Tensor] = None,
+                 f32_out: bool = False, stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
+    """C[g] = A[g] @ B[g] for A [G,M,K] and Bt [G,N,K] (each B[g] passed transposed).
+
+    Operand packing of the reference's _run_ggb
+    (test/gpu/blackwell/grouped_gemm.jl:185-232): groups stacked along the row axis.
+    """
+    _require_cuda(a, bt)
+    if a.dtype != torch.bfloat16 or bt.dtype != torch.bfloat16:
+        raise ValueError("gemm_grouped takes bf16 operands")
+    if a.dim() != 3 or bt.dim() != 3 or a.shape[0] != bt.shape[0] or a.shape[2] != bt.shape[2]:
+        raise ValueError("gemm_grouped takes A[G,M,K] and Bt[G,N,K]")
+    G, M, K = a.shape
+    N = bt.shape[1]
+    if out is None:
+        out = torch.empty((G, M, N), device=a.device, dtype=torch.float32 if f32_out else torch.bfloat16)
+    else:
+        _require_cuda(out)
+        if tuple(out.shape) != (G, M, N):
+            raise ValueError("out must be [G,M,N]")
+    rc = native.lib().gemm_bf16_grouped(_ptr(out), _ptr(a), _ptr(bt), G, M, N, K, N,
+                                        native.GEMM_F32_OUT if f32_out else 0, _stream(stream))
+    native.check(rc)
+    return out
+
+
+def _rowwise_check(x: torch.Tensor, *vecs: torch.Tensor) -> None:
+    _require_cuda(x, *vecs)
+    if x.dtype != torch.float32 or x.dim() != 2 or any(v.dtype != torch.float32 for v in vecs):
+        raise ValueError("row-wise ops take a [rows, N] float32 matrix (and [N] float32 vectors)")
+    if any(v.numel() != x.shape[1] for v in vecs):
+        raise ValueError("weight / bias length must equal N")
+
+
+def softmax(x: torch.Tensor, *, out: Optional[torch.Tensor] = None,
+            stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
+    """Row-wise softmax of a [rows, N] float32 matrix (test/gpu/softmax.jl:151-163)."""
+    _rowwise_check(x)
+    out = torch.empty_like(x) if out is None else out
+    native.check(native.lib().softmax_f32(_ptr(out), _ptr(x), x.shape[0], x.shape[1], _stream(stream)))
+    return out
+
+
+def rms_norm(x: torch.Tensor, w: torch.Tensor, eps: float = 1e-6, *, out: Optional[torch.Tensor] = None,
+             stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
+    """y = x * w / sqrt(mean(x^2) + eps) per row (test/gpu/rms_norm.jl:121-139)."""
+    _rowwise_check(x, w)
+    out = torch.empty_like(x) if out is None else out
+    native.check(native.lib().rms_norm_f32(_ptr(out), _ptr(x), _ptr(w), x.shape[0], x.shape[1],
+                                           ctypes.c_float(eps), _stream(stream)))
+    return out
+
+
+def layer_norm(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor, eps: float = 1e-5, *,
+               out: Optional[torch.Tensor] = None,
+               stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
+    """y = (x - mean) / sqrt(var + eps) * w + bias per row (test/gpu/layer_norm.jl:138-156)."""
+    _rowwise_check(x, w, bias)
+    out = torch.empty_like(x) if out is None else out
+    native.check(native.lib().layer_norm_f32(_ptr(out), _ptr(x), _ptr(w), _ptr(bias), x.shape[0],
+                                             x.shape[1], ctypes.c_float(eps), _stream(stream)))
+    return out
+
+
+def swiglu(gate: torch.Tensor, up: torch.Tensor, *, out: Optional[torch.Tensor] = None,
+           stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
+    """out = silu(gate) * up elementwise, float32 (test/gpu/swiglu.jl:77-98)."""
+    _require_cuda(gate, up)
+    if gate.dtype != torch.float32 or up.dtype != torch.float32 or gate.shape != up.shape:
+        raise ValueError("swiglu takes two float32 tensors of one shape")
+    out = torch.empty_like(gate) if out is None else out
+    native.check(native.lib().swiglu_f32(_ptr(out), _ptr(gate), _ptr(up), gate.numel(), _stream(stream)))
+    return out
+
+
 def selftest(which: int, q=None, k=None, v=None, p=None):
     """Run bring-up probe `which` (see ptxb200_selftest). Returns (out_s, out_o)."""
     dev = torch.device("cuda", torch.cuda.current_device())

@@ -52,6 +52,12 @@ def test_host_side_argument_checks(pkg):
     assert L.gemm_bf16(p, p, p, 128, 128, 100, 128, 0, None) == n.E_SHAPE
     assert L.gemm_bf16(p + 8, p, p, 128, 128, 64, 128, 0, None) == n.E_ALIGN
     assert L.gemm_bf16(p, p, p, 128, 128, 64, 129, 0, None) == n.E_ALIGN     # ldc*2 not 16-B multiple
+    assert L.gemm_bf16_grouped(p, p, None, 2, 128, 64, 64, 64, 0, None) == n.E_INVALID
+    assert L.gemm_bf16_grouped(p, p, p, 0, 128, 64, 64, 64, 0, None) == n.E_INVALID
+    assert L.gemm_bf16_grouped(p, p, p, 2, 128, 32, 64, 32, 0, None) == n.E_SHAPE
+    assert L.gemm_bf16_grouped(p, p, p, 2, 64, 64, 64, 64, 0, None) == n.E_SHAPE
+    assert L.gemm_bf16_grouped(p, p, p, 1 << 20, 1 << 12, 64, 64, 64, 0, None) == n.E_SHAPE
+    assert L.gemm_bf16_grouped(p, p, p, 2, 128, 64, 64, 68, 0, None) == n.E_ALIGN
     assert L.fa_fwd_bf16(p, p, p, None, 1, 1, 256, 128, sc, 0, 0, None, None) == n.E_INVALID
     assert L.fa_fwd_bf16(p, p, p, p, 1, 1, 256, 128, ctypes.c_float(0.0), 0, 0, None, None) == n.E_INVALID
     assert L.fa_fwd_bf16(p, p, p, p, 1, 1, 192, 128, sc, 0, 0, None, None) == n.E_SHAPE

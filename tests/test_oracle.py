@@ -94,3 +94,23 @@ def test_known_answers_file_is_consistent():
         | 1 << s["fixed_bit"] | known["layout_codes"]["B128"] << s["layout_shift"]
     assert val == int(known["sdesc_kmajor_b128"], 16)
     assert known["mma_probe_ones_k16"] == 16.0 and known["accum_probe_4x"] == 64.0
+
+
+def test_rowwise_oracles_known_answers(oracle_mod):
+    """Closed-form cases of the row-wise references (their only pins: the reference's
+    tests hold tolerances, not vectors)."""
+    o = oracle_mod
+    N = 64
+    np.testing.assert_allclose(o.softmax_ref_numpy(np.zeros((3, N), np.float32)), 1.0 / N, rtol=1e-7)
+    x = np.log(np.arange(1, 5, dtype=np.float64)).astype(np.float32)[None, :]
+    np.testing.assert_allclose(o.softmax_ref_numpy(x), np.arange(1, 5)[None, :] / 10.0, rtol=1e-6)
+    ones = np.ones((2, N), np.float32)
+    w = np.linspace(0.5, 1.5, N).astype(np.float32)
+    np.testing.assert_allclose(o.rms_norm_ref_numpy(3 * ones, w, 0.0), np.broadcast_to(w, (2, N)), rtol=1e-6)
+    ramp = np.tile(np.array([-1.0, 1.0], np.float32), N // 2)[None, :]          # mean 0, variance 1
+    b = np.full(N, 0.25, np.float32)
+    np.testing.assert_allclose(o.layer_norm_ref_numpy(ramp + 5.0, w, b, 0.0), ramp * w + b, rtol=1e-6)
+    g = np.array([0.0, np.log(3.0), -np.log(3.0)], np.float32)
+    u = np.array([2.0, 2.0, 2.0], np.float32)
+    np.testing.assert_allclose(o.swiglu_ref_numpy(g, u), [0.0, 2 * np.log(3.0) * 0.75, -2 * np.log(3.0) * 0.25],
+                               rtol=1e-6, atol=1e-7)
