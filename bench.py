@@ -40,11 +40,19 @@ WORKLOADS = {
     "c4": (8, 32, 8192, 128, True, 0.5, 20260004),
 }
 GEMM_WORKLOADS = {"c5": (8192, 8192, 8192, 20260005)}   # M, N (per GPU), K, seed; entries U[-1,1]
+# Row-wise fp32 neighbours of the attention path (not BASELINE configs; HBM-bound, reported in
+# GB/s of algorithmic bytes): name -> (rows, N, seed); 1 GiB in, 1 GiB out per launch.
+ROWWISE_WORKLOADS = {"softmax": (65536, 4096, 20260011), "rms_norm": (65536, 4096, 20260012),
+                     "layer_norm": (65536, 4096, 20260013), "swiglu": (65536, 4096, 20260014)}
 # DRAM traffic of one launch (dram__bytes_read.sum + dram__bytes_write.sum) from the
 # ncu captures summarised in profiles/fa_fwd_d128_c2.md and profiles/gemm_bf16_c5.md;
 # None where no capture was taken.
-NCU_TRAFFIC_BYTES = {"c2": 201.38e6 + 42.33e6, "c3": None, "c4": None, "c5": 985.51e6 + 125.86e6}
+# (softmax: captured at rows = 16384 and scaled by 4 to the bench's 65536 rows, every row being
+# read and written once: profiles/rowwise_softmax_n4096.md)
+NCU_TRAFFIC_BYTES = {"c2": 201.38e6 + 42.33e6, "c3": None, "c4": None, "c5": 985.51e6 + 125.86e6,
+                     "softmax": 4 * (268.45e6 + 218.52e6)}
 FALLBACK_PEAK_TFLOPS = 1590.0
+FALLBACK_PEAK_GBS = 6650.0
 
 
 def host_threads():
@@ -72,6 +80,43 @@ def measured_peak(region_ms):
         return float(mp["bf16_tflops"]), "measured (burst cuBLAS bf16)"
     except Exception:
         return FALLBACK_PEAK_TFLOPS, "fallback"
+
+
+def measured_hbm_peak():
+    """HBM copy bandwidth to divide by (GB/s): the pool's measured STREAM-style copy."""
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured (copy)"
+    except Exception:
+        return FALLBACK_PEAK_GBS, "fallback"
+
+
+def rowwise_cpu(workload, x, w, b):
+    """The oracle's float64 restatement of the reference's CPU reference for `workload`."""
+    import oracle
+    if workload == "softmax":
+        return oracle.softmax_ref_numpy(x)
+    if workload == "rms_norm":
+        return oracle.rms_norm_ref_numpy(x, w, 1e-6)
+    if workload == "layer_norm":
+        return oracle.layer_norm_ref_numpy(x, w, b, 1e-5)
+    return oracle.swiglu_ref_numpy(x, w)
+
+
+def rowwise_cpu_sample(workload, sample_rows):
+    """Times the numpy oracle on `sample_rows` rows of the workload (one thread)."""
+    import numpy as np
+    rows, N, seed = ROWWISE_WORKLOADS[workload]
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal((sample_rows, N)).astype(np.float32)
+    w = rng.standard_normal(N).astype(np.float32) if workload != "swiglu" else \
+        rng.standard_normal((sample_rows, N)).astype(np.float32)
+    b = rng.standard_normal(N).astype(np.float32)
+    t = time.perf_counter()
+    rowwise_cpu(workload, x, w, b)
+    dt = time.perf_counter() - t
+    nbytes = (3 if workload == "swiglu" else 2) * sample_rows * N * 4
+    return nbytes / dt / 1e9, dt
 
 
 class ClockSampler(threading.Thread):
@@ -157,6 +202,23 @@ def run_reference_arm(args):
     import numpy as np
     import oracle
     oracle.build_c_oracle()
+    if args.workload in ROWWISE_WORKLOADS:
+        rows, N, seed = ROWWISE_WORKLOADS[args.workload]
+        sample_rows = 4096
+        for _ in range(min(args.warmup, 1)):
+            rowwise_cpu_sample(args.workload, sample_rows)
+        vals = [rowwise_cpu_sample(args.workload, sample_rows) for _ in range(min(args.steps, 20))]
+        gbs = statistics.median(v[0] for v in vals)
+        dt = statistics.median(v[1] for v in vals)
+        sample = f"{sample_rows} of {rows} rows of N={N} per step, numpy float64 restatement of the reference's CPU reference"
+        print(json.dumps({
+            "impl": "reference", "metric": f"{args.workload} GB/s (fp32 in, fp32 out, algorithmic bytes)",
+            "value": gbs, "unit": "GB/s", "n_gpus": args.gpus, "steps": len(vals), "warmup": min(args.warmup, 1),
+            "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f64", "data": "synthetic", "config": {"workload": f"{args.workload}: rows={rows} N={N}", "sample": sample},
+            "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": 1, "kind": "port", "sample": sample},
+            "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}), flush=True)
+        return
     if args.workload in GEMM_WORKLOADS:
         # bounded sample: a 512 x 512 block of C over the full K (the reference's _ghb_cpu_ref)
         M, N, K, seed = GEMM_WORKLOADS[args.workload]
@@ -228,7 +290,38 @@ def run_native_arm(args):
     ops = pkg.ops
     pkg.native.lib()   # fail loudly here if the CUDA library is missing
 
-    if args.workload in GEMM_WORKLOADS:
+    unit, unit_scale, bound = "TFLOPS", 1e12, "tensor"
+    if args.workload in ROWWISE_WORKLOADS:
+        # this rank's block of rows (world * rows in all): independent rows, no collective
+        rows, N, seed = ROWWISE_WORKLOADS[args.workload]
+        rows = args.rows or rows
+        g = torch.Generator(device=dev).manual_seed(seed + rank)
+        x = torch.randn(rows, N, device=dev, generator=g)
+        w = torch.randn(N, device=dev, generator=g) * 0.1 + 1.0
+        bias = torch.randn(N, device=dev, generator=g) * 0.1
+        o = torch.empty_like(x)
+        if args.workload == "swiglu":
+            inputs = [x, torch.randn(rows, N, device=dev, generator=g)]
+        else:
+            inputs = [x]
+        algo_bytes = (len(inputs) + 1) * rows * N * 4
+        flops_rank = float(algo_bytes)   # the unit of work of this family is the algorithmic byte
+        unit, unit_scale, bound = "GB/s", 1e9, "hbm"
+        metric = f"{args.workload} GB/s (fp32 in, fp32 out, algorithmic bytes), rows={rows} N={N} per GPU"
+        wl_text = f"{args.workload}: rows={rows} N={N} fp32 per GPU, sharded by rows"
+        l2_text = f"input+output {algo_bytes >> 20} MiB per launch > 126 MB L2, no explicit flush"
+        rw_name = args.workload
+
+        def run(ins, out, stream=None):
+            if rw_name == "softmax":
+                ops.softmax(ins[0], out=out, stream=stream)
+            elif rw_name == "rms_norm":
+                ops.rms_norm(ins[0], w, 1e-6, out=out, stream=stream)
+            elif rw_name == "layer_norm":
+                ops.layer_norm(ins[0], w, bias, 1e-5, out=out, stream=stream)
+            else:
+                ops.swiglu(ins[0], ins[1], out=out, stream=stream)
+    elif args.workload in GEMM_WORKLOADS:
         # C[M, N*world] = A[M,K] B[K, N*world]: A replicated, this rank owns one block of N columns
         M, N, K, seed = GEMM_WORKLOADS[args.workload]
         g = torch.Generator(device=dev).manual_seed(seed)
@@ -295,7 +388,7 @@ def run_native_arm(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     region_ms_max = float(t[0])
     ms_per_step = region_ms_max / args.steps
-    value = flops_rank * world / (ms_per_step * 1e-3) / 1e12
+    value = flops_rank * world / (ms_per_step * 1e-3) / unit_scale
 
     # ---- end to end: host buffers in, host buffer out, copies inside the timed region ----
     e2e_steps = max(3, min(args.steps, 10))
@@ -342,7 +435,7 @@ def run_native_arm(args):
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_ms_step = float(t[0]) / e2e_steps
-    e2e_value = flops_rank * world / (e2e_ms_step * 1e-3) / 1e12
+    e2e_value = flops_rank * world / (e2e_ms_step * 1e-3) / unit_scale
     e2e_ok = bool(torch.equal(h_out[(e2e_steps - 1) % nbuf].to(dev), o))
     h2d_bytes = sum(t.numel() * t.element_size() for t in inputs)
     d2h_bytes = o.numel() * o.element_size()
@@ -357,21 +450,22 @@ def run_native_arm(args):
         dist.all_reduce(cs)
 
     if rank == 0:
-        peak, peak_kind = measured_peak(region_ms_max)
-        achieved = flops_rank / (ms_per_step * 1e-3) / 1e12   # one launch on one GPU
+        peak, peak_kind = measured_peak(region_ms_max) if bound == "tensor" else measured_hbm_peak()
+        achieved = flops_rank / (ms_per_step * 1e-3) / unit_scale   # one launch on one GPU
         line = {
-            "metric": metric, "value": value, "unit": "TFLOPS", "n_gpus": world, "steps": args.steps,
+            "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16" if bound == "tensor" else "f32", "data": "synthetic",
             "config": {"workload": wl_text, "l2": l2_text,
                        "seed": seed, "parallelism": f"dp{world} (independent shards, no collective)"},
-            "per_gpu_tflops": value / world,
-            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                         "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
+            "per_gpu_tflops" if bound == "tensor" else "per_gpu_gbs": value / world,
+            "roofline": {"bound": bound, "achieved": achieved, "peak": peak,
+                         "unit": "TFLOP/s" if bound == "tensor" else "GB/s",
+                         "frac": achieved / peak, "traffic": None if args.rows else NCU_TRAFFIC_BYTES.get(args.workload),
                          "peak_kind": peak_kind,
-                         "algorithmic_flops_per_launch": flops_rank,
+                         "algorithmic_flops_per_launch": flops_rank if bound == "tensor" else None,
                          "algorithmic_bytes_per_launch": algo_bytes},
-            "e2e": {"value": e2e_value, "unit": "TFLOPS", "h2d_bytes_per_step": h2d_bytes,
+            "e2e": {"value": e2e_value, "unit": unit, "h2d_bytes_per_step": h2d_bytes,
                     "d2h_bytes_per_step": d2h_bytes, "ms_per_step": e2e_ms_step, "steps": e2e_steps,
                     "matches_resident_run": e2e_ok},
             "gpu_launches": args.steps,
@@ -384,6 +478,10 @@ def run_native_arm(args):
             line["cpu_baseline"] = {"value": cpu_tf, "unit": "TFLOPS", "cores": threads, "kind": "port",
                                     "sample": f"{n_slices} of {B * H} (batch, head) slices of the workload, "
                                               f"{cpu_s:.2f} s wall"}
+        if world == 1 and not args.no_cpu_baseline and args.workload in ROWWISE_WORKLOADS:
+            cpu_gbs, cpu_s = rowwise_cpu_sample(args.workload, 16384)
+            line["cpu_baseline"] = {"value": cpu_gbs, "unit": "GB/s", "cores": 1, "kind": "port",
+                                    "sample": f"16384 of {rows} rows of the workload, numpy float64, {cpu_s:.2f} s wall"}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
@@ -396,8 +494,11 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", choices=["native", "reference"], default="native")
-    ap.add_argument("--workload", choices=sorted(WORKLOADS) + sorted(GEMM_WORKLOADS), default="c2")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS) + sorted(GEMM_WORKLOADS) + sorted(ROWWISE_WORKLOADS),
+                    default="c2")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--rows", type=int, default=0,
+                    help="row-wise workloads only: rows per GPU instead of the default (for small profiler captures)")
     args = ap.parse_args()
     if args.gpus > 1 and "WORLD_SIZE" not in os.environ:
         # launched without torchrun: start one process per GPU ourselves
