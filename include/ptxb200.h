@@ -44,6 +44,9 @@ extern "C" {
 
 /* gemm_bf16 flags */
 #define PTXB200_GEMM_F32_OUT 0x1u /* write C as fp32 (the reference kernel's output type) */
+#define PTXB200_GEMM_NO_SPLIT 0x2u /* never cut tiles along K: every C element is one
+                                      accumulation in k order whatever the tile count
+                                      (see "Few tiles, long K" at gemm_bf16) */
 
 /* fa_fwd_bf16 flags */
 #define PTXB200_FA_NO_LAZY_RESCALE 0x1u /* rescale O on every row-max increase (no 2^8 slack) */
@@ -69,6 +72,15 @@ const char* ptxb200_last_cuda_error(void);
  *
  * Shape contract: M % 128 == 0, N % 128 == 0, K % 64 == 0, all > 0;
  * ldc * sizeof(element) % 16 == 0.
+ *
+ * Few tiles, long K: when the 128x256 output tiles number at most half the SMs and
+ * K is long enough, every tile is cut along K and shared by at least twice as many
+ * SMs; the partial sums meet in fp32 scratch that the library keeps per (device,
+ * stream), allocated by the first launch that needs it (about 38 MB) and freed by
+ * ptxb200_shutdown, and a second small kernel on the same stream adds them up.
+ * Results stay reproducible from launch to launch; they differ in the last bits from
+ * the unsplit summation order, which PTXB200_GEMM_NO_SPLIT keeps. No reference
+ * counterpart (test/gpu/blackwell/gemm_highperf_blackwell.jl:27-32 leaves it).
  *
  * Replaces the reference's _run_ghb launch of _ghb_gemm_kernel! /
  * _ghb_persistent_kernel! (test/gpu/blackwell/gemm_highperf_blackwell.jl:69-199,

@@ -50,6 +50,7 @@ int current_ctx(DeviceCtx** out) {
 }
 
 int release_all_ctx() {
+  gemm_release_scratch();
   std::lock_guard<std::mutex> lock(g_mu);
   int prev = -1;
   cudaGetDevice(&prev);
@@ -150,7 +151,7 @@ int gemm_bf16(void* C, const void* A, const void* Bt, int M, int N, int K, int l
               void* stream) {
   if (C == nullptr || A == nullptr || Bt == nullptr) return PTXB200_E_INVALID;
   if (M <= 0 || N <= 0 || K <= 0 || ldc < N) return PTXB200_E_INVALID;
-  if (flags & ~PTXB200_GEMM_F32_OUT) return PTXB200_E_INVALID;
+  if (flags & ~(PTXB200_GEMM_F32_OUT | PTXB200_GEMM_NO_SPLIT)) return PTXB200_E_INVALID;
   if (M % 128 != 0 || N % 128 != 0 || K % 64 != 0) return PTXB200_E_SHAPE;
   const size_t esz = (flags & PTXB200_GEMM_F32_OUT) ? 4 : 2;
   if (!aligned16(C) || !aligned16(A) || !aligned16(Bt) || ((size_t)ldc * esz) % 16 != 0)
@@ -165,7 +166,7 @@ int gemm_bf16_grouped(void* C, const void* A, const void* Bt, int G, int M, int 
                       unsigned flags, void* stream) {
   if (C == nullptr || A == nullptr || Bt == nullptr) return PTXB200_E_INVALID;
   if (G <= 0 || M <= 0 || N <= 0 || K <= 0 || ldc < N) return PTXB200_E_INVALID;
-  if (flags & ~PTXB200_GEMM_F32_OUT) return PTXB200_E_INVALID;
+  if (flags & ~(PTXB200_GEMM_F32_OUT | PTXB200_GEMM_NO_SPLIT)) return PTXB200_E_INVALID;
   if (M % 128 != 0 || N % 64 != 0 || K % 64 != 0) return PTXB200_E_SHAPE;
   if ((long long)G * M >= (1ll << 31) || (long long)G * N >= (1ll << 31)) return PTXB200_E_SHAPE;
   const size_t esz = (flags & PTXB200_GEMM_F32_OUT) ? 4 : 2;

@@ -28,8 +28,22 @@
 // rows brings in the next group's rows (or zero fill past the end); those columns
 // are computed and never stored.
 //
+// Few tiles, long K (the reference leaves this: one tile per CTA,
+// gemm_highperf_blackwell.jl:27-32). With fewer tiles than half the SMs the launch would
+// run on a fraction of the machine, so the tiles are cut along K: their k-iterations
+// form one line that is dealt out evenly to at least twice as many CTAs, a CTA's share
+// being a run of whole tiles with a partial tile at either end. A partial accumulator
+// is parked in a slab of fp32 scratch, and a second small kernel sums each tile's slabs
+// in segment order and writes C. The order of the sums is fixed, so results are
+// reproducible from launch to launch (they differ in the last bits from the unsplit
+// order).
+//
 // Algorithmic work per launch: 2*G*M*N*K flop; compulsory bytes G*((M*K + N*K)*2 +
 // M*N*sizeof(out)).
+#include <map>
+#include <mutex>
+#include <utility>
+
 #include "host_common.h"
 #include "sm100_prims.cuh"
 
@@ -71,11 +85,64 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
   tn = r / rows_in_band;
 }
 
+// The work of one CTA: first its whole tiles of the data-parallel part (tile =
+// blockIdx.x + i * gridDim.x below dp_tiles), then its share [it, end) of the
+// k-iteration line of the stream-K tiles. The three roles walk the same sequence.
+struct Sched {
+  int dp_tiles;        // tiles handed out whole
+  int sk_tiles;        // tiles cut along K (tile indices dp_tiles .. dp_tiles + sk_tiles - 1)
+  int sk_ctas;         // CTAs that share the k-iteration line (the first sk_ctas of the grid)
+  int kiters;          // K / kBK
+  float* slabs;        // [2 * sk_ctas][kBM * kBN] fp32 partial accumulators
+};
+struct Unit {
+  int tile;            // global tile index
+  int k0, k1;          // k-iterations [k0, k1) of that tile
+  int slab;            // partial units: which of this CTA's two slabs (0: its share starts here, 1: not)
+};
+struct UnitIter {
+  int i = 0;
+  long long it = 0, end = 0, begin = 0;
+  __device__ __forceinline__ void init(const Sched& s) {
+    const long long total = (long long)s.sk_tiles * s.kiters;
+    if ((int)blockIdx.x < s.sk_ctas) {
+      begin = it = total * blockIdx.x / s.sk_ctas;
+      end = total * (blockIdx.x + 1) / s.sk_ctas;
+    }
+  }
+  __device__ __forceinline__ bool next(const Sched& s, Unit& u) {
+    const int tile = blockIdx.x + i * gridDim.x;
+    if (tile < s.dp_tiles) {
+      ++i;
+      u = {tile, 0, s.kiters, 0};
+      return true;
+    }
+    if (it < end) {
+      const int t = (int)(it / s.kiters);
+      const int k0 = (int)(it - (long long)t * s.kiters);
+      const long long left = end - it;
+      const int len = left < s.kiters - k0 ? (int)left : s.kiters - k0;
+      u = {s.dp_tiles + t, k0, k0 + len, it == begin ? 0 : 1};
+      it += len;
+      return true;
+    }
+    return false;
+  }
+};
+// CTA whose share of the stream-K line holds iteration x: the largest c with
+// floor(c * total / ctas) <= x.
+__device__ __forceinline__ int sk_owner(long long x, long long total, int ctas) {
+  return (int)(((x + 1) * ctas - 1) / total);
+}
+// Slab element of accumulator (row, col): 16-byte column groups outermost, rows
+// innermost, so that a warp's 32 rows of one group are 512 contiguous bytes.
+__device__ __forceinline__ size_t slab_index(int row, int col4) { return ((size_t)col4 * kBM + row) * 4; }
+
 template <bool kF32Out>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
             void* __restrict__ c_out, int M, int N, int K, int ldc, int groups,
-            uint32_t* status) {
+            const Sched sched, uint32_t* status) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (base - smem_u32(smem_raw));
@@ -117,8 +184,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   const int tiles_m = M / kBM;
   const int tiles_n = (N + kBN - 1) / kBN;
   const int tiles_per_group = tiles_m * tiles_n;
-  const int total_tiles = tiles_per_group * groups;
-  const int kiters = K / kBK;
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -126,13 +191,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       tma_prefetch_desc(&tmap_a);
       tma_prefetch_desc(&tmap_b);
       uint32_t it = 0;
-      for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+      UnitIter units;
+      units.init(sched);
+      Unit u;
+      while (units.next(sched, u)) {
         int tm, tn;
-        const int g = tile / tiles_per_group;
-        tile_coords(tile - g * tiles_per_group, tiles_m, tiles_n, tm, tn);
+        const int g = u.tile / tiles_per_group;
+        tile_coords(u.tile - g * tiles_per_group, tiles_m, tiles_n, tm, tn);
         const int a_row = g * M + tm * kBM;
         const int b_row = g * N + tn * kBN;
-        for (int k = 0; k < kiters; ++k, ++it) {
+        for (int k = u.k0; k < u.k1; ++k, ++it) {
           const uint32_t s = it % kStages;
           const uint32_t ph = (it / kStages) & 1u;
           mbar_wait(bar_empty + 8 * s, ph ^ 1u, wctx, kSiteEmpty);
@@ -149,13 +217,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     {
       constexpr uint32_t idesc = make_idesc_bf16_f32(kBM, kBN, false, false);
       uint32_t it = 0, t = 0;
-      for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++t) {
+      UnitIter units;
+      units.init(sched);
+      Unit u;
+      for (; units.next(sched, u); ++t) {
         const uint32_t buf = t & 1u;
         const uint32_t aph = (t >> 1) & 1u;
         mbar_wait_warp(bar_acc_empty + 8 * buf, aph ^ 1u, wctx, kSiteAccEmpty);
         tc_fence_after();
         const uint32_t d_tmem = tmem + buf * kAccCols;
-        for (int k = 0; k < kiters; ++k, ++it) {
+        for (int k = u.k0; k < u.k1; ++k, ++it) {
           const uint32_t s = it % kStages;
           const uint32_t ph = (it / kStages) & 1u;
           mbar_wait_warp(bar_full + 8 * s, ph, wctx, kSiteFull);
@@ -166,7 +237,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 #pragma unroll
           for (int kk = 0; kk < kBK / 16; ++kk) {
             // +32 bytes (2 descriptor units) per 16-element K step inside the swizzle row
-            tc_mma_ss_warp(d_tmem, da + 2 * kk, dhi, db + 2 * kk, dhi, idesc, (k | kk) != 0 ? 1u : 0u);
+            tc_mma_ss_warp(d_tmem, da + 2 * kk, dhi, db + 2 * kk, dhi, idesc,
+                           (k != u.k0 || kk != 0) ? 1u : 0u);
           }
           tc_commit_warp(bar_empty + 8 * s);   // slot free once these MMAs have read it
         }
@@ -177,11 +249,33 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     // ---------------- epilogue: warps 2..5 ----------------
     const int quad = warp & 3;                       // TMEM lane quadrant this warp may touch
     const int row_in_tile = quad * 32 + lane;
+    // 32 accumulator columns of one row -> C
+    auto store_chunk = [&](size_t row, int col, const uint32_t (&v)[32]) {
+      if (kF32Out) {
+        float* dst = reinterpret_cast<float*>(c_out) + row * (size_t)ldc + col;
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          st_global_v4(dst + 4 * i, v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+      } else {
+        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(c_out) + row * (size_t)ldc + col;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const uint32_t p0 = pack_bf16x2(__uint_as_float(v[8 * i + 0]), __uint_as_float(v[8 * i + 1]));
+          const uint32_t p1 = pack_bf16x2(__uint_as_float(v[8 * i + 2]), __uint_as_float(v[8 * i + 3]));
+          const uint32_t p2 = pack_bf16x2(__uint_as_float(v[8 * i + 4]), __uint_as_float(v[8 * i + 5]));
+          const uint32_t p3 = pack_bf16x2(__uint_as_float(v[8 * i + 6]), __uint_as_float(v[8 * i + 7]));
+          st_global_v4(dst + 8 * i, p0, p1, p2, p3);
+        }
+      }
+    };
     uint32_t t = 0;
-    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++t) {
+    UnitIter units;
+    units.init(sched);
+    Unit u;
+    for (; units.next(sched, u); ++t) {
       int tm, tn;
-      const int g = tile / tiles_per_group;
-      tile_coords(tile - g * tiles_per_group, tiles_m, tiles_n, tm, tn);
+      const int g = u.tile / tiles_per_group;
+      tile_coords(u.tile - g * tiles_per_group, tiles_m, tiles_n, tm, tn);
       const uint32_t buf = t & 1u;
       const uint32_t aph = (t >> 1) & 1u;
       mbar_wait(bar_acc_full + 8 * buf, aph, wctx, kSiteAccFull);
@@ -189,32 +283,35 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       const size_t row = (size_t)g * M + (size_t)tm * kBM + row_in_tile;
       const int col0 = tn * kBN;
       const uint32_t t_row = tmem_addr(tmem, quad * 32, buf * kAccCols);
+      const bool whole = u.k0 == 0 && u.k1 == sched.kiters;
+      if (whole) {
+#pragma unroll 1
+        for (int c = 0; c < kBN / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld32(t_row + c * 32, v);
+          tc_wait_ld_bind(v);
+          const int col = col0 + c * 32;
+          if (col < N) store_chunk(row, col, v);
+        }
+        // every TMEM read of this accumulator has completed (wait::ld above)
+        tc_fence_before();
+        mbar_arrive(bar_acc_empty + 8 * buf);
+        continue;
+      }
+      // ---- a part of a tile cut along K: park the partial sums; sk_reduce_kernel adds
+      // the parts up in segment order and writes C
+      float* slab = sched.slabs + (size_t)(2 * blockIdx.x + u.slab) * (kBM * kBN);
 #pragma unroll 1
       for (int c = 0; c < kBN / 32; ++c) {
         uint32_t v[32];
         tmem_ld32(t_row + c * 32, v);
         tc_wait_ld_bind(v);
-        const int col = col0 + c * 32;
-        if (col < N) {
-          if (kF32Out) {
-            float* dst = reinterpret_cast<float*>(c_out) + row * (size_t)ldc + col;
 #pragma unroll
-            for (int i = 0; i < 8; ++i)
-              st_global_v4(dst + 4 * i, v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-          } else {
-            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(c_out) + row * (size_t)ldc + col;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const uint32_t p0 = pack_bf16x2(__uint_as_float(v[8 * i + 0]), __uint_as_float(v[8 * i + 1]));
-              const uint32_t p1 = pack_bf16x2(__uint_as_float(v[8 * i + 2]), __uint_as_float(v[8 * i + 3]));
-              const uint32_t p2 = pack_bf16x2(__uint_as_float(v[8 * i + 4]), __uint_as_float(v[8 * i + 5]));
-              const uint32_t p3 = pack_bf16x2(__uint_as_float(v[8 * i + 6]), __uint_as_float(v[8 * i + 7]));
-              st_global_v4(dst + 8 * i, p0, p1, p2, p3);
-            }
-          }
-        }
+        for (int i = 0; i < 8; ++i)
+          __stcg(reinterpret_cast<float4*>(slab + slab_index(row_in_tile, c * 8 + i)),
+                 make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
+                             __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3])));
       }
-      // every TMEM read of this accumulator has completed (wait::ld above)
       tc_fence_before();
       mbar_arrive(bar_acc_empty + 8 * buf);
     }
@@ -228,7 +325,83 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   }
 }
 
+// Second step of a launch that cut tiles along K: C = sum of each tile's parts, in
+// segment order. One thread per (tile, row, 4 columns); consecutive threads take
+// consecutive rows, which is the contiguous axis of the slabs.
+template <bool kF32Out>
+__global__ void __launch_bounds__(256)
+sk_reduce_kernel(void* __restrict__ c_out, int M, int N, int ldc, int tiles_m, int tiles_n,
+                 const Sched sched) {
+  const int tiles_per_group = tiles_m * tiles_n;
+  const long long total = (long long)sched.sk_tiles * sched.kiters;
+  const long long n_items = (long long)sched.sk_tiles * (kBN / 4) * kBM;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < n_items;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const int r = (int)(idx % kBM);
+    const int col4 = (int)((idx / kBM) % (kBN / 4));
+    const int t_local = (int)(idx / ((long long)kBM * (kBN / 4)));
+    const int tile = sched.dp_tiles + t_local;
+    int tm, tn;
+    const int g = tile / tiles_per_group;
+    tile_coords(tile - g * tiles_per_group, tiles_m, tiles_n, tm, tn);
+    const int col = tn * kBN + col4 * 4;
+    if (col >= N) continue;
+    const long long x0 = (long long)t_local * sched.kiters;
+    const int c_first = sk_owner(x0, total, sched.sk_ctas);
+    const int nseg = sk_owner(x0 + sched.kiters - 1, total, sched.sk_ctas) - c_first + 1;
+    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (int seg = 0; seg < nseg; ++seg) {
+      const int cta = c_first + seg;
+      const long long cta_begin = total * cta / sched.sk_ctas;
+      const float* part = sched.slabs + (size_t)(2 * cta + (cta_begin >= x0 ? 0 : 1)) * (kBM * kBN);
+      const float4 q = __ldcg(reinterpret_cast<const float4*>(part + slab_index(r, col4)));
+      acc.x += q.x; acc.y += q.y; acc.z += q.z; acc.w += q.w;
+    }
+    const size_t row = (size_t)g * M + (size_t)tm * kBM + r;
+    if (kF32Out) {
+      *reinterpret_cast<float4*>(reinterpret_cast<float*>(c_out) + row * (size_t)ldc + col) = acc;
+    } else {
+      uint2 pk;
+      pk.x = pack_bf16x2(acc.x, acc.y);
+      pk.y = pack_bf16x2(acc.z, acc.w);
+      *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(c_out) + row * (size_t)ldc + col) = pk;
+    }
+  }
+}
+
 }  // namespace
+
+namespace {
+
+// fp32 slabs for tiles cut along K, one set per (device, stream): launches on one
+// stream run one after the other, launches on different streams may overlap and must
+// not share them. Allocated on the first launch that needs them, freed by
+// ptxb200_shutdown.
+std::mutex g_sk_mu;
+std::map<std::pair<int, cudaStream_t>, float*> g_sk;
+
+int sk_scratch(const DeviceCtx& ctx, cudaStream_t stream, float** out) {
+  std::lock_guard<std::mutex> lock(g_sk_mu);
+  float*& slabs = g_sk[{ctx.device, stream}];
+  if (slabs == nullptr)
+    PTXB200_CUDA_TRY(cudaMalloc((void**)&slabs, (size_t)2 * ctx.sm_count * kBM * kBN * sizeof(float)));
+  *out = slabs;
+  return PTXB200_OK;
+}
+
+constexpr int kSkMinIters = 8;   // a CTA's share of the k-iteration line is at least this long
+
+}  // namespace
+
+void gemm_release_scratch() {
+  std::lock_guard<std::mutex> lock(g_sk_mu);
+  int prev = -1;
+  cudaGetDevice(&prev);
+  for (auto& kv : g_sk)
+    if (kv.second != nullptr && cudaSetDevice(kv.first.first) == cudaSuccess) cudaFree(kv.second);
+  g_sk.clear();
+  if (prev >= 0) cudaSetDevice(prev);
+}
 
 int launch_gemm(const DeviceCtx& ctx, void* C, const void* A, const void* Bt, int groups, int M, int N,
                 int K, int ldc, unsigned flags, cudaStream_t stream) {
@@ -238,8 +411,31 @@ int launch_gemm(const DeviceCtx& ctx, void* C, const void* A, const void* Bt, in
   rc = encode_tmap_bf16_2d(&tb, Bt, (uint64_t)groups * N, (uint64_t)K, (uint64_t)K * 2, kBN, kBK);
   if (rc != PTXB200_OK) return rc;
 
-  const int tiles = groups * (M / kBM) * ((N + kBN - 1) / kBN);
-  const int grid = tiles < ctx.sm_count ? tiles : ctx.sm_count;
+  const int tiles_m = M / kBM, tiles_n = (N + kBN - 1) / kBN;
+  const int tiles = groups * tiles_m * tiles_n;
+  Sched sched;
+  sched.kiters = K / kBK;
+  sched.dp_tiles = tiles;
+  sched.sk_tiles = 0;
+  sched.sk_ctas = 0;
+  sched.slabs = nullptr;
+  int grid = tiles < ctx.sm_count ? tiles : ctx.sm_count;
+  // Few tiles, long K: cut every tile along K so that at least twice as many CTAs work.
+  // (Cutting only the tiles of a sparse LAST wave was built too and measured slower
+  // than leaving them whole: parking and re-reading two partial tiles per CTA costs
+  // more than the idle SMs of that wave.)
+  if (!(flags & PTXB200_GEMM_NO_SPLIT) && tiles * 2 <= ctx.sm_count) {
+    const long long line = (long long)tiles * sched.kiters;
+    long long ctas = line / kSkMinIters;
+    if (ctas > ctx.sm_count) ctas = ctx.sm_count;
+    if (ctas >= 2 * tiles) {
+      if ((rc = sk_scratch(ctx, stream, &sched.slabs)) != PTXB200_OK) return rc;
+      sched.dp_tiles = 0;
+      sched.sk_tiles = tiles;
+      sched.sk_ctas = (int)ctas;
+      grid = (int)ctas;
+    }
+  }
   uint32_t* status = ctx.workspace + kWsStatus;
   if (flags & PTXB200_GEMM_F32_OUT) {
     static bool attr_done_f32[64] = {false};
@@ -248,7 +444,7 @@ int launch_gemm(const DeviceCtx& ctx, void* C, const void* A, const void* Bt, in
                                             cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
       attr_done_f32[ctx.device & 63] = true;
     }
-    gemm_kernel<true><<<grid, kThreads, kSmemBytes, stream>>>(ta, tb, C, M, N, K, ldc, groups, status);
+    gemm_kernel<true><<<grid, kThreads, kSmemBytes, stream>>>(ta, tb, C, M, N, K, ldc, groups, sched, status);
   } else {
     static bool attr_done_bf16[64] = {false};
     if (!attr_done_bf16[ctx.device & 63]) {
@@ -256,9 +452,18 @@ int launch_gemm(const DeviceCtx& ctx, void* C, const void* A, const void* Bt, in
                                             cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
       attr_done_bf16[ctx.device & 63] = true;
     }
-    gemm_kernel<false><<<grid, kThreads, kSmemBytes, stream>>>(ta, tb, C, M, N, K, ldc, groups, status);
+    gemm_kernel<false><<<grid, kThreads, kSmemBytes, stream>>>(ta, tb, C, M, N, K, ldc, groups, sched, status);
   }
   PTXB200_CUDA_TRY(cudaGetLastError());
+  if (sched.sk_tiles > 0) {
+    const long long items = (long long)sched.sk_tiles * (kBN / 4) * kBM;
+    const int rgrid = (int)((items + 255) / 256);
+    if (flags & PTXB200_GEMM_F32_OUT)
+      sk_reduce_kernel<true><<<rgrid, 256, 0, stream>>>(C, M, N, ldc, tiles_m, tiles_n, sched);
+    else
+      sk_reduce_kernel<false><<<rgrid, 256, 0, stream>>>(C, M, N, ldc, tiles_m, tiles_n, sched);
+    PTXB200_CUDA_TRY(cudaGetLastError());
+  }
   return PTXB200_OK;
 }
 

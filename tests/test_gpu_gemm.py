@@ -115,8 +115,9 @@ def test_grouped_gemm_equals_per_group_calls(pkg, gpu):
     bt = (torch.randn(G, N, K, generator=g) * 0.1).to(torch.bfloat16).to(gpu)
     bt[3] = float("nan")   # group 3's B: only group 3's C may see it
     buf = torch.full((G * M, N + 32), 7.0, dtype=torch.float32, device=gpu)
+    # NO_SPLIT: with tiles cut along K the summation order depends on the tile count
     rc = pkg.native.lib().gemm_bf16_grouped(buf.data_ptr(), a.data_ptr(), bt.data_ptr(), G, M, N, K,
-                                            N + 32, pkg.native.GEMM_F32_OUT,
+                                            N + 32, pkg.native.GEMM_F32_OUT | pkg.native.GEMM_NO_SPLIT,
                                             torch.cuda.current_stream().cuda_stream)
     assert rc == 0 and pkg.ops.sync_status() == 0
     assert torch.all(buf[:, N:] == 7.0)
@@ -126,7 +127,73 @@ def test_grouped_gemm_equals_per_group_calls(pkg, gpu):
             assert torch.isnan(got[i]).all()
             continue
         # N = 192 is outside gemm_bf16's N % 128 contract: compare on a 128-column slice
-        one = pkg.ops.gemm(a[i], bt[i, :128].contiguous(), f32_out=True)
+        one = pkg.ops.gemm(a[i], bt[i, :128].contiguous(), f32_out=True, no_split=True)
         assert torch.equal(got[i][:, :128], one)
         assert torch.isfinite(got[i]).all()
     assert pkg.ops.sync_status() == 0
+
+
+# ---------------------------------------------------------------------------
+# Tiles cut along K (no reference counterpart): at most half as many tiles as SMs,
+# K long enough for the split to pay.
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("M,N,K", [
+    (128, 256, 8192),     # one tile shared by 16 CTAs
+    (128, 128, 4096),     # one ragged tile
+    (256, 512, 4096),     # 4 tiles, 32 CTAs, 8 iterations each
+    (384, 768, 2048),     # 9 tiles: shares cross tile boundaries unevenly
+    (1024, 1024, 8192),   # 32 tiles on 148 CTAs: most CTAs hold two partial tiles
+    (1152, 2048, 4096),   # 72 tiles, just under half the SMs
+    (2048, 4096, 8192),   # 256 tiles: not split (the flag then changes nothing)
+])
+@pytest.mark.parametrize("f32_out", [True, False])
+def test_gemm_split_tail_matches_oracle_and_unsplit(pkg, gpu, oracle_mod, M, N, K, f32_out):
+    g = torch.Generator().manual_seed(M + N + K)
+    a = (torch.randn(M, K, generator=g) * 0.1).to(torch.bfloat16)
+    bt = (torch.randn(N, K, generator=g) * 0.1).to(torch.bfloat16)
+    a_d, bt_d = a.to(gpu), bt.to(gpu)
+    c = pkg.ops.gemm(a_d, bt_d, f32_out=f32_out)
+    c_again = pkg.ops.gemm(a_d, bt_d, f32_out=f32_out)
+    c_whole = pkg.ops.gemm(a_d, bt_d, f32_out=f32_out, no_split=True)
+    assert pkg.ops.sync_status() == 0
+    assert torch.equal(c, c_again)                       # fixed summation order: reproducible
+    # against the unsplit order: fp32 re-association only
+    torch.testing.assert_close(c.float(), c_whole.float(), rtol=2 ** -7 if not f32_out else 1e-4, atol=1e-3)
+    if M * N * K <= 2 ** 33:
+        ref = oracle_mod.gemm_ref_c(bits(a), bits(bt))
+        got = c.float().cpu().numpy()
+        if f32_out:
+            np.testing.assert_allclose(got, ref, rtol=1e-4, atol=1e-4)
+        else:
+            np.testing.assert_allclose(got, ref, rtol=2 ** -7, atol=1e-3)
+
+
+def test_grouped_gemm_split_tail(pkg, gpu):
+    """Groups and the K split compose: 10 groups x 3 tiles shared by 148 CTAs."""
+    G, M, N, K = 10, 128, 768, 4096
+    g = torch.Generator().manual_seed(77)
+    a = (torch.randn(G, M, K, generator=g) * 0.1).to(torch.bfloat16).to(gpu)
+    bt = (torch.randn(G, N, K, generator=g) * 0.1).to(torch.bfloat16).to(gpu)
+    c = pkg.ops.gemm_grouped(a, bt, f32_out=True)
+    ref = torch.bmm(a.float(), bt.float().transpose(1, 2))
+    assert pkg.ops.sync_status() == 0
+    torch.testing.assert_close(c, ref, rtol=1e-4, atol=1e-3)
+
+
+def test_gemm_split_on_two_streams(pkg, gpu):
+    """Scratch is per stream: split launches that overlap on two streams stay correct."""
+    M, N, K = 256, 512, 8192
+    g = torch.Generator().manual_seed(9)
+    a = (torch.randn(M, K, generator=g) * 0.1).to(torch.bfloat16).to(gpu)
+    bts = [(torch.randn(N, K, generator=g) * 0.1).to(torch.bfloat16).to(gpu) for _ in range(2)]
+    want = [pkg.ops.gemm(a, bt, f32_out=True) for bt in bts]
+    torch.cuda.synchronize()
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    outs = [torch.empty(M, N, device=gpu) for _ in range(2)]
+    for _ in range(20):
+        for st, bt, o in zip(streams, bts, outs):
+            pkg.ops.gemm(a, bt, out=o, f32_out=True, stream=st)
+    torch.cuda.synchronize()
+    assert pkg.ops.sync_status() == 0
+    for o, w in zip(outs, want):
+        assert torch.equal(o, w)
