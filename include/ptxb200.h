@@ -47,6 +47,7 @@ extern "C" {
 #define PTXB200_GEMM_NO_SPLIT 0x2u /* never cut tiles along K: every C element is one
                                       accumulation in k order whatever the tile count
                                       (see "Few tiles, long K" at gemm_bf16) */
+#define PTXB200_GEMM_ONE_CTA 0x4u  /* always the one-CTA-per-tile kernel, never the CTA-pair one */
 
 /* fa_fwd_bf16 flags */
 #define PTXB200_FA_NO_LAZY_RESCALE 0x1u /* rescale O on every row-max increase (no 2^8 slack) */

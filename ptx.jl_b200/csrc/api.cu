@@ -134,7 +134,8 @@ const char* ptxb200_strerror(int code) {
         "?",            "gemm:empty",    "gemm:full",    "gemm:acc_empty", "gemm:acc_full",
         "fa:load.q_free", "fa:load.kv_free", "fa:mma.q_full", "fa:mma.kv_full", "fa:mma.p_full",
         "fa:mma.o_ready", "fa:softmax.s_full", "fa:corr.alpha", "fa:corr.l_ready",
-        "fa:corr.o_done", "probe", "-", "fa:shared memory base not 1024-byte aligned",
+        "fa:corr.o_done", "probe", "-", "shared memory base not 1024-byte aligned",
+        "gemm2:empty", "gemm2:full", "gemm2:acc_empty", "gemm2:acc_full",
     };
     unsigned site = ((unsigned)code >> 8) & 0xFFu;
     const char* name = site < sizeof(sites) / sizeof(sites[0]) ? sites[site] : "?";
@@ -151,7 +152,7 @@ int gemm_bf16(void* C, const void* A, const void* Bt, int M, int N, int K, int l
               void* stream) {
   if (C == nullptr || A == nullptr || Bt == nullptr) return PTXB200_E_INVALID;
   if (M <= 0 || N <= 0 || K <= 0 || ldc < N) return PTXB200_E_INVALID;
-  if (flags & ~(PTXB200_GEMM_F32_OUT | PTXB200_GEMM_NO_SPLIT)) return PTXB200_E_INVALID;
+  if (flags & ~(PTXB200_GEMM_F32_OUT | PTXB200_GEMM_NO_SPLIT | PTXB200_GEMM_ONE_CTA)) return PTXB200_E_INVALID;
   if (M % 128 != 0 || N % 128 != 0 || K % 64 != 0) return PTXB200_E_SHAPE;
   const size_t esz = (flags & PTXB200_GEMM_F32_OUT) ? 4 : 2;
   if (!aligned16(C) || !aligned16(A) || !aligned16(Bt) || ((size_t)ldc * esz) % 16 != 0)
@@ -166,7 +167,7 @@ int gemm_bf16_grouped(void* C, const void* A, const void* Bt, int G, int M, int 
                       unsigned flags, void* stream) {
   if (C == nullptr || A == nullptr || Bt == nullptr) return PTXB200_E_INVALID;
   if (G <= 0 || M <= 0 || N <= 0 || K <= 0 || ldc < N) return PTXB200_E_INVALID;
-  if (flags & ~(PTXB200_GEMM_F32_OUT | PTXB200_GEMM_NO_SPLIT)) return PTXB200_E_INVALID;
+  if (flags & ~(PTXB200_GEMM_F32_OUT | PTXB200_GEMM_NO_SPLIT | PTXB200_GEMM_ONE_CTA)) return PTXB200_E_INVALID;
   if (M % 128 != 0 || N % 64 != 0 || K % 64 != 0) return PTXB200_E_SHAPE;
   if ((long long)G * M >= (1ll << 31) || (long long)G * N >= (1ll << 31)) return PTXB200_E_SHAPE;
   const size_t esz = (flags & PTXB200_GEMM_F32_OUT) ? 4 : 2;

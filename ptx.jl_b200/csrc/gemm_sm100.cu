@@ -405,6 +405,9 @@ void gemm_release_scratch() {
 
 int launch_gemm(const DeviceCtx& ctx, void* C, const void* A, const void* Bt, int groups, int M, int N,
                 int K, int ldc, unsigned flags, cudaStream_t stream) {
+  // enough 256x256 tiles for every pair of SMs: the CTA-pair kernel (gemm2_sm100.cu)
+  if (!(flags & PTXB200_GEMM_ONE_CTA) && gemm_pair_eligible(ctx, groups, M, N, K))
+    return launch_gemm_pair(ctx, C, A, Bt, groups, M, N, K, ldc, flags, stream);
   CUtensorMap ta, tb;
   int rc = encode_tmap_bf16_2d(&ta, A, (uint64_t)groups * M, (uint64_t)K, (uint64_t)K * 2, kBM, kBK);
   if (rc != PTXB200_OK) return rc;

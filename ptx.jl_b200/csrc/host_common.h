@@ -62,6 +62,10 @@ int launch_gemm(const DeviceCtx& ctx, void* C, const void* A, const void* Bt, in
 int launch_fa_fwd(const DeviceCtx& ctx, void* O, void* lse, const void* Q, const void* K,
                   const void* V, int B, int H, int H_kv, int S, int D, float sm_scale, int causal,
                   unsigned flags, void* dbg, uint32_t* status, cudaStream_t stream);
+// CTA-pair GEMM (gemm2_sm100.cu): whether it applies to a shape, and its launcher.
+bool gemm_pair_eligible(const DeviceCtx& ctx, int groups, int M, int N, int K);
+int launch_gemm_pair(const DeviceCtx& ctx, void* C, const void* A, const void* Bt, int groups, int M, int N,
+                     int K, int ldc, unsigned flags, cudaStream_t stream);
 // Frees the stream-K scratch of every (device, stream) that used it.
 void gemm_release_scratch();
 // Row-wise fp32 kernels; op: 0 softmax, 1 RMS norm, 2 layer norm.

@@ -72,7 +72,7 @@ def fa_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: bool = 
 
 
 def gemm(a: torch.Tensor, bt: torch.Tensor, *, out: Optional[torch.Tensor] = None,
-         f32_out: bool = False, no_split: bool = False,
+         f32_out: bool = False, no_split: bool = False, one_cta: bool = False,
          stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
     """C[M,N] = A[M,K] @ B[K,N] with B passed column-major, i.e. as Bt = B^T [N,K].
 
@@ -91,14 +91,15 @@ def gemm(a: torch.Tensor, bt: torch.Tensor, *, out: Optional[torch.Tensor] = Non
     else:
         _require_cuda(out)
     ldc = out.stride(0)
-    flags = (native.GEMM_F32_OUT if f32_out else 0) | (native.GEMM_NO_SPLIT if no_split else 0)
+    flags = ((native.GEMM_F32_OUT if f32_out else 0) | (native.GEMM_NO_SPLIT if no_split else 0)
+             | (native.GEMM_ONE_CTA if one_cta else 0))
     rc = native.lib().gemm_bf16(_ptr(out), _ptr(a), _ptr(bt), M, N, K, ldc, flags, _stream(stream))
     native.check(rc)
     return out
 
 
 def gemm_grouped(a: torch.Tensor, bt: torch.Tensor, *, out: Optional[torch.Tensor] = None,
-                 f32_out: bool = False, no_split: bool = False,
+                 f32_out: bool = False, no_split: bool = False, one_cta: bool = False,
                  stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
     """C[g] = A[g] @ B[g] for A [G,M,K] and Bt [G,N,K] (each B[g] passed transposed).
 
@@ -118,7 +119,8 @@ def gemm_grouped(a: torch.Tensor, bt: torch.Tensor, *, out: Optional[torch.Tenso
         _require_cuda(out)
         if tuple(out.shape) != (G, M, N):
             raise ValueError("out must be [G,M,N]")
-    flags = (native.GEMM_F32_OUT if f32_out else 0) | (native.GEMM_NO_SPLIT if no_split else 0)
+    flags = ((native.GEMM_F32_OUT if f32_out else 0) | (native.GEMM_NO_SPLIT if no_split else 0)
+             | (native.GEMM_ONE_CTA if one_cta else 0))
     rc = native.lib().gemm_bf16_grouped(_ptr(out), _ptr(a), _ptr(bt), G, M, N, K, N, flags, _stream(stream))
     native.check(rc)
     return out

@@ -197,3 +197,45 @@ def test_gemm_split_on_two_streams(pkg, gpu):
     assert pkg.ops.sync_status() == 0
     for o, w in zip(outs, want):
         assert torch.equal(o, w)
+
+
+# ---------------------------------------------------------------------------
+# CTA-pair kernel (256x256 tile per pair of SMs, tcgen05.mma.cta_group::2): taken when
+# M % 256 == 0 and there are at least 74 such tiles. Same k-order per output element
+# as the one-CTA kernel, so the two must agree bit for bit.
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("M,N,K", [
+    (2048, 4096, 1024),   # 8 x 16 tiles: two rounds for most pairs
+    (4096, 2176, 256),    # N % 256 == 128: zero-filled half boxes, guarded stores
+    (2560, 2048, 64),     # a single k-iteration per tile (ring shorter than its depth)
+    (8192, 8192, 512),    # 1024 tiles
+])
+@pytest.mark.parametrize("f32_out", [True, False])
+def test_gemm_pair_kernel_equals_one_cta_kernel(pkg, gpu, oracle_mod, M, N, K, f32_out):
+    g = torch.Generator().manual_seed(M * 3 + N * 5 + K)
+    a = (torch.randn(M, K, generator=g) * 0.1).to(torch.bfloat16)
+    bt = (torch.randn(N, K, generator=g) * 0.1).to(torch.bfloat16)
+    a_d, bt_d = a.to(gpu), bt.to(gpu)
+    c_pair = pkg.ops.gemm(a_d, bt_d, f32_out=f32_out)
+    c_one = pkg.ops.gemm(a_d, bt_d, f32_out=f32_out, one_cta=True)
+    assert pkg.ops.sync_status() == 0
+    assert torch.equal(c_pair, c_one)
+    if M * N * K <= 2 ** 33:
+        ref = oracle_mod.gemm_ref_c(bits(a), bits(bt))
+        got = c_pair.float().cpu().numpy()
+        if f32_out:
+            np.testing.assert_allclose(got, ref, rtol=1e-4, atol=1e-4)
+        else:
+            np.testing.assert_allclose(got, ref, rtol=2 ** -7, atol=1e-3)
+
+
+def test_grouped_gemm_pair_kernel(pkg, gpu):
+    G, M, N, K = 4, 1024, 1280, 256     # 4 x 4 x 5 = 80 tiles of 256 x 256
+    g = torch.Generator().manual_seed(21)
+    a = (torch.randn(G, M, K, generator=g) * 0.1).to(torch.bfloat16).to(gpu)
+    bt = (torch.randn(G, N, K, generator=g) * 0.1).to(torch.bfloat16).to(gpu)
+    c_pair = pkg.ops.gemm_grouped(a, bt, f32_out=True)
+    c_one = pkg.ops.gemm_grouped(a, bt, f32_out=True, one_cta=True)
+    assert pkg.ops.sync_status() == 0
+    assert torch.equal(c_pair, c_one)
+    torch.testing.assert_close(c_pair, torch.bmm(a.float(), bt.float().transpose(1, 2)), rtol=1e-4, atol=1e-3)
