@@ -49,7 +49,7 @@ ROWWISE_WORKLOADS = {"softmax": (65536, 4096, 20260011), "rms_norm": (65536, 409
 # None where no capture was taken.
 # (softmax: captured at rows = 16384 and scaled by 4 to the bench's 65536 rows, every row being
 # read and written once: profiles/rowwise_softmax_n4096.md)
-NCU_TRAFFIC_BYTES = {"c2": 201.38e6 + 42.33e6, "c3": None, "c4": None, "c5": 985.51e6 + 125.86e6,
+NCU_TRAFFIC_BYTES = {"c2": 201.38e6 + 42.33e6, "c3": None, "c4": None, "c5": 1067.3e6 + 131.1e6,
                      "softmax": 4 * (268.45e6 + 218.52e6)}
 FALLBACK_PEAK_TFLOPS = 1590.0
 FALLBACK_PEAK_GBS = 6650.0

@@ -42,7 +42,10 @@ constexpr int kBStage2 = 128 * kBK2 * 2;       // this CTA's 128 rows of B^T: 16
 constexpr int kStage2 = kAStage2 + kBStage2;
 constexpr int kThreads2 = 192;
 constexpr int kAccCols2 = 256;
-constexpr int kGroupM2 = 8;                    // row-tiles (of 256) per rasterisation band
+#ifndef PTXB200_GEMM2_GROUP_M
+#define PTXB200_GEMM2_GROUP_M 8
+#endif
+constexpr int kGroupM2 = PTXB200_GEMM2_GROUP_M;   // row-tiles (of 256) per rasterisation band
 
 constexpr int kOffA2 = 0;
 constexpr int kOffB2 = kOffA2 + kStages2 * kAStage2;
