@@ -5,8 +5,8 @@
   python bench.py --impl reference --gpus N --steps K ...  (CPU reference arm)
 
 A "step" is one pass of the hot path over one batch of synthetic input: one
-fa_fwd_bf16 launch on this rank's shard. At N = 1 the workload is BASELINE
-config 2 (B=4, H=16, S=4096, D=128, non-causal, bf16, N(0,1) inputs). At N > 1
+fa_fwd_bf16 launch on this rank's shard. At N = 1 the workload is the headline
+configuration (B=4, H=16, S=4096, D=128, non-causal, bf16, N(0,1) inputs). At N > 1
 each rank holds one such shard of a batch N times larger, split by
 (batch x head) with no collective on the data path ("weak" scaling); one process
 per GPU, launched by torch.distributed.run.
@@ -40,7 +40,7 @@ WORKLOADS = {
     "c4": (8, 32, 8192, 128, True, 0.5, 20260004),
 }
 GEMM_WORKLOADS = {"c5": (8192, 8192, 8192, 20260005)}   # M, N (per GPU), K, seed; entries U[-1,1]
-# Row-wise fp32 neighbours of the attention path (not BASELINE configs; HBM-bound, reported in
+# Row-wise fp32 neighbours of the attention path (not headline configurations; HBM-bound, reported in
 # GB/s of algorithmic bytes): name -> (rows, N, seed); 1 GiB in, 1 GiB out per launch.
 ROWWISE_WORKLOADS = {"softmax": (65536, 4096, 20260011), "rms_norm": (65536, 4096, 20260012),
                      "layer_norm": (65536, 4096, 20260013), "swiglu": (65536, 4096, 20260014)}

@@ -50,7 +50,7 @@ def make_gemm(name, M, N, K, seed):
 
 
 if __name__ == "__main__":
-    # BASELINE config 1: B=1 H=4 S=256 D=64, N(0,1), seed 20260001
+    # the CPU-runnable reference configuration: B=1 H=4 S=256 D=64, N(0,1), seed 20260001
     make_attention("attn_b1_h4_s256_d64", 1, 4, 256, 64, 20260001, 1.0)
     # a D=128 case at the reference's smallest test shape and input scale
     make_attention("attn_b1_h1_s256_d128", 1, 1, 256, 128, 7919 + 131 + 256, 0.5)

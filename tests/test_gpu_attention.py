@@ -86,7 +86,7 @@ def test_large_logits_do_not_overflow(pkg, gpu, oracle_mod):
 
 @pytest.mark.parametrize("causal", [False, True])
 def test_full_size_properties(pkg, gpu, causal):
-    """Size-independent properties at a BASELINE-sized slice (S = 4096, D = 128):
+    """Size-independent properties at a headline-sized slice (S = 4096, D = 128):
     with V = all ones every output is exactly 1 (rows of P sum to 1); with one-hot
     structure in V the output rows are convex combinations, so 0 <= O <= 1; and a
     second launch on the same inputs is bit-identical (no race)."""
