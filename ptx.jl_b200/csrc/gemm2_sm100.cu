@@ -174,7 +174,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
-  const int tiles_m = M / kBM2;
+  const int tiles_m = (M + kBM2 - 1) / kBM2;   // M % 128 == 0: the last row-tile may be its first half only
   const int tiles_n = (N + kBN2 - 1) / kBN2;
   const int tiles_per_group = tiles_m * tiles_n;
   const int total_tiles = tiles_per_group * groups;
@@ -253,6 +253,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       mbar_wait(bar_acc_full + 8 * buf, aph, wctx, kSite2AccFull);
       tc_fence_after();
       const size_t row = (size_t)g * M + (size_t)tm * kBM2 + rank * 128 + row_in_half;
+      // in a half-filled last row-tile the peer's 128 rows lie past M (its A box read the
+      // next group's rows or zero fill): computed, not stored
+      const bool rows_valid = tm * kBM2 + (int)rank * 128 < M;
       const int col0 = tn * kBN2;
       const uint32_t t_row = tmem_addr(tmem, quad * 32, buf * kAccCols2);
 #pragma unroll 1
@@ -261,7 +264,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         tmem_ld32(t_row + c * 32, v);
         tc_wait_ld_bind(v);
         const int col = col0 + c * 32;
-        if (col < N) {
+        if (col < N && rows_valid) {
           if (kF32Out) {
             float* dst = reinterpret_cast<float*>(c_out) + row * (size_t)ldc + col;
 #pragma unroll
@@ -300,9 +303,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
 bool gemm_pair_eligible(const DeviceCtx& ctx, int groups, int M, int N, int K) {
   (void)K;
-  if (M % kBM2 != 0) return false;
-  // worth it once every pair of SMs has a tile
-  const long long tiles = (long long)groups * (M / kBM2) * ((N + kBN2 - 1) / kBN2);
+  // worth it once every pair of SMs has a tile (M % 128 == 0 is the entry points' contract;
+  // a last row-tile may be half-filled)
+  const long long tiles = (long long)groups * ((M + kBM2 - 1) / kBM2) * ((N + kBN2 - 1) / kBN2);
   return tiles >= ctx.sm_count / 2;
 }
 
@@ -313,7 +316,7 @@ int launch_gemm_pair(const DeviceCtx& ctx, void* C, const void* A, const void* B
   if (rc != PTXB200_OK) return rc;
   rc = encode_tmap_bf16_2d(&tb, Bt, (uint64_t)groups * N, (uint64_t)K, (uint64_t)K * 2, 128, kBK2);
   if (rc != PTXB200_OK) return rc;
-  const long long tiles = (long long)groups * (M / kBM2) * ((N + kBN2 - 1) / kBN2);
+  const long long tiles = (long long)groups * ((M + kBM2 - 1) / kBM2) * ((N + kBN2 - 1) / kBN2);
   const int max_pairs = ctx.sm_count / 2;
   const int pairs = tiles < max_pairs ? (int)tiles : max_pairs;
   uint32_t* status = ctx.workspace + kWsStatus;

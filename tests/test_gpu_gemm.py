@@ -201,13 +201,14 @@ def test_gemm_split_on_two_streams(pkg, gpu):
 
 # ---------------------------------------------------------------------------
 # CTA-pair kernel (256x256 tile per pair of SMs, tcgen05.mma.cta_group::2): taken when
-# M % 256 == 0 and there are at least 74 such tiles. Same k-order per output element
+# there are at least 74 such tiles (the last row-tile may be half-filled). Same k-order per output element
 # as the one-CTA kernel, so the two must agree bit for bit.
 # ---------------------------------------------------------------------------
 @pytest.mark.parametrize("M,N,K", [
     (2048, 4096, 1024),   # 8 x 16 tiles: two rounds for most pairs
     (4096, 2176, 256),    # N % 256 == 128: zero-filled half boxes, guarded stores
     (2560, 2048, 64),     # a single k-iteration per tile (ring shorter than its depth)
+    (2432, 2304, 128),    # M % 256 == 128: the last row-tile is half-filled (peer rows not stored)
     (8192, 8192, 512),    # 1024 tiles
 ])
 @pytest.mark.parametrize("f32_out", [True, False])
@@ -230,7 +231,7 @@ def test_gemm_pair_kernel_equals_one_cta_kernel(pkg, gpu, oracle_mod, M, N, K, f
 
 
 def test_grouped_gemm_pair_kernel(pkg, gpu):
-    G, M, N, K = 4, 1024, 1280, 256     # 4 x 4 x 5 = 80 tiles of 256 x 256
+    G, M, N, K = 4, 1152, 1280, 256     # 4 x 5 x 5 = 100 tiles of 256 x 256, each group's last row-tile half-filled
     g = torch.Generator().manual_seed(21)
     a = (torch.randn(G, M, K, generator=g) * 0.1).to(torch.bfloat16).to(gpu)
     bt = (torch.randn(G, N, K, generator=g) * 0.1).to(torch.bfloat16).to(gpu)
