@@ -273,6 +273,13 @@ def run_reference_arm(args):
 
 # --------------------------------------------------------------------------- native arm
 def run_native_arm(args):
+    # stdout carries exactly one line, the JSON record: libraries that write to file
+    # descriptor 1 (NCCL prints its version there when a communicator is created) are
+    # sent to stderr for the duration of the run
+    sys.stdout.flush()
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
+
     import torch
     import torch.distributed as dist
     import __graft_entry__ as ge
@@ -482,7 +489,7 @@ def run_native_arm(args):
             cpu_gbs, cpu_s = rowwise_cpu_sample(args.workload, 16384)
             line["cpu_baseline"] = {"value": cpu_gbs, "unit": "GB/s", "cores": 1, "kind": "port",
                                     "sample": f"16384 of {rows} rows of the workload, numpy float64, {cpu_s:.2f} s wall"}
-        print(json.dumps(line), flush=True)
+        os.write(json_fd, (json.dumps(line) + "\n").encode())
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
