@@ -92,14 +92,6 @@ enum : uint32_t {
   kSiteCorrLReady = 13, kSiteCorrODone = 14
 };
 
-// Unrolling of the MMA-issue thread's loops (its code runs once per tile, between
-// long stretches of other warps' code).
-#ifdef PTXB200_FA_MMA_ROLLED
-#define FA_MMA_UNROLL _Pragma("unroll 1")
-#else
-#define FA_MMA_UNROLL _Pragma("unroll")
-#endif
-
 // Timestamp hooks for offline latency studies; compiled out of the product build.
 #ifdef PTXB200_FA_TIMING
 #define FA_TSTAMP(cond, rec, tile, ev)                                            \
@@ -225,11 +217,8 @@ __device__ __forceinline__ void fa_mma_role(const FaParams& p, uint32_t base, ui
   auto qk = [&](int stage, uint32_t KS) {
     const uint32_t qa = q_smem + stage * T::kTileBytes;
     const uint32_t ka = kv_smem + KS * T::kTileBytes;
-FA_MMA_UNROLL
+#pragma unroll
     for (int kk = 0; kk < T::kQKAtoms; ++kk)
-#if defined(PTXB200_FA_ABLATE) && (PTXB200_FA_ABLATE == 5 || PTXB200_FA_ABLATE == 6)
-      if (kk < 0)
-#endif
       if (kConv)
         tc_mma_ss_warp(tmem + C::kColS + stage * 128, T::kmajor_lo(qa, kk), T::kKMajorHi,
                        T::kmajor_lo(ka, kk), T::kKMajorHi, T::kIdescQK, kk != 0 ? 1u : 0u);
@@ -243,15 +232,12 @@ FA_MMA_UNROLL
   // exponentiated (the reference's split-P idea, flash_attention_defs.jl:36-50).
   auto pv = [&](int stage, uint32_t VS, bool accumulate, uint32_t parity) {
     const uint32_t va = kv_smem + VS * T::kTileBytes;
-FA_MMA_UNROLL
+#pragma unroll
     for (int h = 0; h < 2; ++h) {
       wait(bar(C::kBarPFull + 2 * stage + h), parity, kSiteMmaPFull);
       tc_fence_after();
-FA_MMA_UNROLL
+#pragma unroll
       for (int kk = 4 * h; kk < 4 * h + 4; ++kk)
-#if defined(PTXB200_FA_ABLATE) && (PTXB200_FA_ABLATE == 4 || PTXB200_FA_ABLATE == 6)
-        if (kk < 0)
-#endif
         if (kConv)
           tc_mma_ts_warp(tmem + C::kColO + stage * D, T::p_tmem(tmem, C::kColS + stage * 128, kk),
                          T::v_lo(va, kk), T::kVHi, T::kIdescPV, (accumulate || kk != 0) ? 1u : 0u);
@@ -283,7 +269,7 @@ FA_MMA_UNROLL
     if (has_next)
       wait(bar(C::kBarKvFull + KS), KS == 0 ? (ring_ph ^ 1u) : ring_ph, kSiteMmaKvFull);
     FA_TSTAMP(stamp_lane && blockIdx.x == 0 && item_i == 0, 2, j, 7);
-FA_MMA_UNROLL
+#pragma unroll
     for (int s = 0; s < 2; ++s) {
       if (!kCausal || j < nt[s]) {
         FA_TSTAMP(stamp_lane && blockIdx.x == 0 && item_i == 0, 2, j, 3 * s + 0);
@@ -399,12 +385,8 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
           const uint32_t s = kv_it % C::kSlots;
           const uint32_t ph = (kv_it / C::kSlots) & 1u;
           mbar_wait(bar(C::kBarKvFree + s), ph ^ 1u, wctx, kSiteLoadKvFree);
-#if defined(PTXB200_FA_ABLATE) && PTXB200_FA_ABLATE == 7
-          mbar_arrive(bar(C::kBarKvFull + s));   // no data movement: measures everything but the loads
-#else
           mbar_arrive_expect_tx(bar(C::kBarKvFull + s), T::kTileBytes);
           T::load(kv_smem + s * T::kTileBytes, tmap, row, bar(C::kBarKvFull + s));
-#endif
           ++kv_it;
         };
         for (int w = blockIdx.x; w < p.total_work; w += gridDim.x, ++item_i) {
@@ -464,14 +446,6 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
         ++cnt_s;
         tc_fence_after();
         FA_TSTAMP(w == 0 && row == 0, stage, j, 1);
-#if defined(PTXB200_FA_ABLATE) && PTXB200_FA_ABLATE == 8
-        stats_neg[stage * 128 + row] = 0.0f;
-        mbar_arrive(bar(C::kBarAlpha + stage));
-        tc_fence_before();
-        mbar_arrive(bar(C::kBarPFull + 2 * stage + 0));
-        mbar_arrive(bar(C::kBarPFull + 2 * stage + 1));
-        continue;
-#endif
         uint32_t v[4][32];
 #pragma unroll
         for (int c = 0; c < 4; ++c) tmem_ld32(t_row + c * 32, v[c]);
@@ -538,24 +512,14 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
               if ((kEmuMask >> (b + i)) & 1u) {
                 e[i] = exp2_poly2(x[i]);
               } else {
-#if defined(PTXB200_FA_ABLATE) && PTXB200_FA_ABLATE >= 3
-                e[i] = __ffma2_rn(x[i], x[i], x[i]);
-#else
                 e[i].x = ex2_approx(x[i].x);
                 e[i].y = ex2_approx(x[i].y);
-#endif
               }
             }
 #pragma unroll
             for (int i = 0; i < kBatch; ++i) {
-#if !(defined(PTXB200_FA_ABLATE) && PTXB200_FA_ABLATE == 2)
               sum2[i & 1] = __fadd2_rn(sum2[i & 1], e[i]);
-#endif
-#if defined(PTXB200_FA_ABLATE) && PTXB200_FA_ABLATE == 1
-              pk[b + i] = __float_as_uint(e[i].x) ^ __float_as_uint(e[i].y);
-#else
               pk[b + i] = pack_bf16x2(e[i].x, e[i].y);
-#endif
             }
           }
           tmem_st16(t_row + c * 16, pk);
