@@ -4,7 +4,8 @@ Both paths shard into independent units, so there is no collective on the data
 path: attention by (batch x head) slices -- the reference's work item is
 (m_block, batch*head) with no coupling between heads
 (test/gpu/blackwell/flash_attention_defs.jl:269-272) -- and the GEMM by contiguous
-blocks of output columns with A replicated. Collectives (torch.distributed: NCCL
+blocks of output columns with A replicated; the row-wise kernels by blocks of rows.
+Collectives (torch.distributed: NCCL
 on GPUs, gloo in the CPU tests) are used only to agree on timings and to gather
 results for verification.
 """
@@ -35,6 +36,12 @@ def gemm_column_shard(N: int, rank: int, world: int, granule: int = 128) -> Tupl
         raise ValueError("N must be a multiple of the column granule")
     b, e = shard_range(N // granule, rank, world)
     return b * granule, e * granule
+
+
+def row_shard(rows: int, rank: int, world: int) -> Tuple[int, int]:
+    """Contiguous block of rows of a row-wise op (softmax, norms, SwiGLU) owned by
+    `rank`: rows are independent, so the shards need no exchange either."""
+    return shard_range(rows, rank, world)
 
 
 def all_shards(total: int, world: int) -> List[Tuple[int, int]]:

@@ -71,8 +71,8 @@ def test_odd_number_of_128_row_blocks(pkg, gpu, oracle_mod, S, D, causal):
     assert mx <= ATTN_MAX_ABS and mean <= ATTN_MEAN_ABS, (mx, mean)
 
 
-def test_baseline_config_1_shape(pkg, gpu, oracle_mod):
-    """B=1 H=4 S=256 D=64 non-causal, N(0,1) inputs: the CPU-runnable baseline case."""
+def test_cpu_runnable_config_shape(pkg, gpu, oracle_mod):
+    """B=1 H=4 S=256 D=64 non-causal, N(0,1) inputs: the configuration sized for a CPU run."""
     mx, mean = _run(pkg, gpu, oracle_mod, 1, 4, 256, 64, False, sigma_qk=1.0, seed=20260001)
     assert mx <= ATTN_MAX_ABS and mean <= ATTN_MEAN_ABS, (mx, mean)
 
@@ -106,6 +106,39 @@ def test_full_size_properties(pkg, gpu, causal):
     if causal:
         # the first query row attends to key 0 only
         assert torch.equal(o1[:, :, 0, :], v[:, :, 0, :])
+
+
+@pytest.mark.parametrize("name,B,H,S,D,causal,sigma", [
+    ("c2", 4, 16, 4096, 128, False, 1.0),
+    ("c3", 16, 16, 2048, 64, False, 1.0),
+    ("c4", 8, 32, 8192, 128, True, 0.5),
+])
+def test_full_size_configs_against_oracle_slices(pkg, gpu, oracle_mod, name, B, H, S, D, causal, sigma):
+    """The three full-size attention configurations, whole on the device, checked on
+    sampled (batch, head) slices: two against the C oracle, eight against an unfused
+    fp32 computation on the GPU (same bf16-quantised inputs, the oracle's formula)."""
+    g = torch.Generator(device=gpu).manual_seed(len(name) * 1000 + S)
+    q = (torch.randn(B, H, S, D, device=gpu, generator=g) * sigma).to(torch.bfloat16)
+    k = (torch.randn(B, H, S, D, device=gpu, generator=g) * sigma).to(torch.bfloat16)
+    v = torch.randn(B, H, S, D, device=gpu, generator=g).to(torch.bfloat16)
+    o = pkg.ops.fa_fwd(q, k, v, causal=causal)
+    assert pkg.ops.sync_status() == 0
+    scale = 1.0 / D ** 0.5
+    slices = [(0, 0), (B - 1, H - 1), (B // 2, 1), (1 % B, H // 2), (B - 1, 0), (0, H - 1), (B // 3, H // 3),
+              ((2 * B) // 3, (2 * H) // 3)]
+    for i, (b, h) in enumerate(slices):
+        qf, kf, vf = q[b, h].float(), k[b, h].float(), v[b, h].float()
+        sc = (qf @ kf.t()) * scale
+        if causal:
+            sc = sc.masked_fill(torch.ones(S, S, dtype=torch.bool, device=gpu).triu(1), float("-inf"))
+        ref = torch.softmax(sc, dim=1) @ vf
+        err = (o[b, h].float() - ref).abs()
+        assert float(err.max()) <= ATTN_MAX_ABS and float(err.mean()) <= ATTN_MEAN_ABS, (name, b, h, float(err.max()))
+        if i < 2:
+            ref_c = oracle_mod.attention_ref_c(bits(q[b, h]).reshape(1, S, D), bits(k[b, h]).reshape(1, S, D),
+                                               bits(v[b, h]).reshape(1, S, D), scale, causal)
+            mx, mean = attn_errors(o[b, h], ref_c)
+            assert mx <= ATTN_MAX_ABS and mean <= ATTN_MEAN_ABS, (name, b, h, mx, mean)
 
 
 @pytest.mark.parametrize("D,causal,H,H_kv", [(128, False, 8, 2), (128, True, 6, 3), (64, False, 4, 1), (64, True, 8, 8)])

@@ -25,6 +25,7 @@ def test_shard_ranges_partition_everything(pkg):
             assert max(sizes) - min(sizes) <= 1
     assert sh.attention_shard(4, 16, 3, 8) == (24, 32)
     assert sh.gemm_column_shard(8192, 7, 8) == (7168, 8192)
+    assert sh.row_shard(65537, 0, 8) == (0, 8193) and sh.row_shard(65537, 7, 8) == (57345, 65537)
     with pytest.raises(ValueError):
         sh.gemm_column_shard(100, 0, 2)
     with pytest.raises(ValueError):
