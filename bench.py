@@ -172,6 +172,28 @@ def physical_gpu_index(local_rank):
     return local_rank
 
 
+def bind_to_gpu_local_cpus(index, pci_bus_id=None):
+    """Multi-GPU runs: run this rank on the CPUs NVML reports as local to its GPU, so the
+    pinned host buffers of the end-to-end leg (first touched by this process) sit on
+    the GPU's own NUMA node and eight ranks do not push their copies over one socket
+    link. Returns how many CPUs the rank ended up with, or None if nothing was changed."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        handle = (pynvml.nvmlDeviceGetHandleByPciBusId(pci_bus_id.encode()) if pci_bus_id
+                  else pynvml.nvmlDeviceGetHandleByIndex(index))
+        words = pynvml.nvmlDeviceGetCpuAffinity(handle, (os.cpu_count() + 63) // 64)
+        local = {64 * w + b for w, word in enumerate(words) for b in range(64) if (word >> b) & 1}
+        allowed = os.sched_getaffinity(0)
+        pick = local & allowed
+        if len(pick) >= 2 and pick != allowed:
+            os.sched_setaffinity(0, pick)
+            return len(pick)
+    except Exception:
+        pass
+    return None
+
+
 # --------------------------------------------------------------------------- CPU arm
 def cpu_sample(workload, n_slices, repeats=1):
     """Times the CPU oracle (C port of the reference's fab_cpu_ref) on `n_slices`
@@ -291,6 +313,12 @@ def run_native_arm(args):
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    local_cpus = None
+    if world > 1:
+        pr = torch.cuda.get_device_properties(local_rank)
+        bus = (f"{pr.pci_domain_id:08x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0"
+               if hasattr(pr, "pci_bus_id") else None)
+        local_cpus = bind_to_gpu_local_cpus(physical_gpu_index(local_rank), bus)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     pkg = ge.load_package()
@@ -474,7 +502,7 @@ def run_native_arm(args):
                          "algorithmic_bytes_per_launch": algo_bytes},
             "e2e": {"value": e2e_value, "unit": unit, "h2d_bytes_per_step": h2d_bytes,
                     "d2h_bytes_per_step": d2h_bytes, "ms_per_step": e2e_ms_step, "steps": e2e_steps,
-                    "matches_resident_run": e2e_ok},
+                    "matches_resident_run": e2e_ok, "rank0_gpu_local_cpus": local_cpus},
             "gpu_launches": args.steps,
             "clocks": sampler.summary(),
             "checksum": {"sum": float(cs[0]), "abs_sum": float(cs[1])},
