@@ -17,7 +17,7 @@
  *     and nothing was launched (see PTXB200_E_*). Device-side trouble (a bounded
  *     wait inside a kernel ran out) never traps or hangs; it is recorded in a
  *     per-device status word that ptxb200_sync_status() returns as a positive
- *     code (0xB2000000 | site << 8 | aux).
+ *     code (0x32000000 | site << 8 | aux).
  *   - All device pointers must be 16-byte aligned (TMA and 128-bit stores).
  *   - Only compute capability 10.x devices are accepted. There is no CPU or
  *     library fallback: on any other device the calls return
@@ -234,8 +234,14 @@ int ptxb200_sync_status(void* stream);
  *      out_o = P V (128xD fp32) with P (bf16, 128x128) read from tensor memory
  *      and V as an MN-major shared-memory operand.
  *   2  the same with D = 64.
+ *   3  a bounded wait that nothing satisfies (the native counterpart of reading the
+ *      reference's beacons after a stuck wait, bench/flash_attention.jl:163-179): one
+ *      thread waits on a barrier nobody arrives on, gives up after the wait limit
+ *      (1.5 s), and the kernel returns. out: 3 uint32 = {0, 0, 0xD0E5} (both waits
+ *      report failure, the kernel reached its end); the next ptxb200_sync_status
+ *      returns the positive code of wait site 15 ("probe").
  * For 1 and 2: q,k,v are (128, D) bf16, p is (128,128) bf16, all row-major.
- * Unused pointers may be NULL for probe 0.
+ * Unused pointers may be NULL for probes 0 and 3.
  */
 int ptxb200_selftest(int which, void* out_s, void* out_o, const void* q, const void* k,
                      const void* v, const void* p, void* stream);

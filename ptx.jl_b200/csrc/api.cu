@@ -6,6 +6,7 @@
 #include <vector>
 
 #include "host_common.h"
+#include "sm100_prims.cuh"
 
 namespace ptxb200 {
 
@@ -128,7 +129,7 @@ const char* ptxb200_strerror(int code) {
     case PTXB200_E_CAPACITY: return "request exceeds a fixed capacity of this entry point";
     default: break;
   }
-  if (code > 0 && ((uint32_t)code & 0xFF000000u) == 0xB2000000u) {
+  if (code > 0 && ((uint32_t)code & 0xFF000000u) == kStatusTimeoutTag) {
     static thread_local char buf[160];
     static const char* const sites[] = {
         "?",            "gemm:empty",    "gemm:full",    "gemm:acc_empty", "gemm:acc_full",
@@ -265,9 +266,9 @@ int ptxb200_sync_status(void* stream) {
 
 int ptxb200_selftest(int which, void* out_s, void* out_o, const void* q, const void* k,
                      const void* v, const void* p, void* stream) {
-  if (which < 0 || which > 2) return PTXB200_E_INVALID;
+  if (which < 0 || which > 3) return PTXB200_E_INVALID;
   if (out_s == nullptr) return PTXB200_E_INVALID;
-  if (which != 0 && (out_o == nullptr || q == nullptr || k == nullptr || v == nullptr || p == nullptr))
+  if (which != 0 && which != 3 && (out_o == nullptr || q == nullptr || k == nullptr || v == nullptr || p == nullptr))
     return PTXB200_E_INVALID;
   if (!aligned16(out_s) || !aligned16(out_o) || !aligned16(q) || !aligned16(k) || !aligned16(v) ||
       !aligned16(p))

@@ -167,6 +167,31 @@ int launch_tile_probe(const DeviceCtx& ctx, void* out_s, void* out_o, const void
   return PTXB200_OK;
 }
 
+// A bounded wait on a barrier that nobody arrives on: the wait gives up after its
+// limit, records its first-blame code (site 15) in the status word and the kernel
+// returns normally. What the host-side reporting is tested against.
+__global__ void __launch_bounds__(32, 1) wait_expiry_kernel(uint32_t* out, uint32_t* status) {
+  __shared__ __align__(8) unsigned long long bar_storage;
+  __shared__ uint32_t abort_word;
+  const uint32_t bar = smem_u32(&bar_storage);
+  if (threadIdx.x == 0) {
+    abort_word = 0;
+    mbar_init(bar, 1);
+    mbar_fence_init();
+  }
+  __syncwarp();
+  const WaitCtx wctx{status, &abort_word};
+  bool ok = true;
+  if (threadIdx.x == 0) ok = mbar_wait(bar, 0, wctx, 15);
+  __syncwarp();
+  // a second wait in the same CTA returns at once through the abort flag
+  bool ok2 = true;
+  if (threadIdx.x == 1) ok2 = mbar_wait(bar, 0, wctx, 15);
+  if (threadIdx.x == 0) out[0] = ok ? 1u : 0u;
+  if (threadIdx.x == 1) out[1] = ok2 ? 1u : 0u;
+  if (threadIdx.x == 0) out[2] = 0xD0E5u;   // the kernel ran to its end
+}
+
 }  // namespace
 
 int launch_selftest(const DeviceCtx& ctx, int which, void* out_s, void* out_o, const void* q,
@@ -178,6 +203,10 @@ int launch_selftest(const DeviceCtx& ctx, int which, void* out_s, void* out_o, c
       return PTXB200_OK;
     case 1: return launch_tile_probe<128>(ctx, out_s, out_o, q, k, v, p, stream);
     case 2: return launch_tile_probe<64>(ctx, out_s, out_o, q, k, v, p, stream);
+    case 3:
+      wait_expiry_kernel<<<1, 32, 0, stream>>>(reinterpret_cast<uint32_t*>(out_s), ctx.workspace + kWsStatus);
+      PTXB200_CUDA_TRY(cudaGetLastError());
+      return PTXB200_OK;
     default: return PTXB200_E_INVALID;
   }
 }

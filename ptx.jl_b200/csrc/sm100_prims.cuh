@@ -86,8 +86,10 @@ __host__ __device__ constexpr uint32_t tmem_addr(uint32_t base, uint32_t lane, u
 static_assert(tmem_addr(0, 5, 0) == (5u << 16), "lane bits sit at [31:16]");
 static_assert(tmem_addr(0x00070000u, 31, 0) == 0x00070000u + 0x1F0000u, "lane 31");
 
-// Status word layout written on a wait that ran out: 0xB2000000 | site<<8 | aux.
-constexpr uint32_t kStatusTimeoutTag = 0xB2000000u;
+// Status word layout written on a wait that ran out: 0x32000000 | site<<8 | aux
+// (top bit clear: the host returns the word as a positive int).
+constexpr uint32_t kStatusTimeoutTag = 0x32000000u;
+static_assert((kStatusTimeoutTag >> 31) == 0, "status codes are positive ints");
 
 #if defined(__CUDACC__)
 

@@ -33,8 +33,9 @@ def test_version_and_strerror(pkg):
         assert lib.ptxb200_strerror(code)
     text = lib.ptxb200_strerror(0xB2000000 - (1 << 32) | 0)  # not a positive code
     assert text
-    timeout = lib.ptxb200_strerror(0x32000B02 | 0)            # wrong tag: unknown
-    assert b"unknown" in timeout
+    assert b"unknown" in lib.ptxb200_strerror(0x42000B02)     # wrong tag
+    timeout = lib.ptxb200_strerror(0x32000B03)                # site 11, cta 1, parity 1
+    assert b"fa:softmax.s_full" in timeout and b"ran out" in timeout
 
 
 def test_host_side_argument_checks(pkg):

@@ -45,3 +45,21 @@ def test_tile_random(pkg, gpu, oracle_mod, which, D):
     o_ref = p.float().numpy() @ v.float().numpy()
     np.testing.assert_allclose(out_s.cpu().numpy(), s_ref, rtol=1e-4, atol=1e-3)
     np.testing.assert_allclose(out_o.cpu().numpy(), o_ref, rtol=1e-4, atol=1e-3)
+
+
+def test_bounded_wait_expiry_is_reported_and_the_device_stays_usable(pkg, gpu):
+    """A wait that nothing satisfies gives up after its limit: the kernel returns, the
+    status word names the wait site, a second wait in the CTA returns at once, and the
+    library keeps working afterwards (no trap, no fault, no hang)."""
+    import time
+    assert pkg.ops.sync_status() == 0
+    t0 = time.perf_counter()
+    out, _ = pkg.ops.selftest(3)
+    status = pkg.ops.sync_status()
+    dt = time.perf_counter() - t0
+    assert 1.0 < dt < 10.0                       # the 1.5 s wait limit, not a hang
+    assert out.cpu().tolist()[:3] == [0, 0, 0xD0E5]
+    assert status > 0 and (status >> 24) == 0x32 and ((status >> 8) & 0xFF) == 15
+    assert "probe" in pkg.native.strerror(status)
+    assert pkg.ops.sync_status() == 0             # reading the status cleared it
+    test_tmem_roundtrip(pkg, gpu)                 # the device is as usable as before
