@@ -152,23 +152,48 @@ struct FaParams {
   int heads_kv;         // key/value heads per batch entry (divides heads_q)
 };
 
-// Work item -> (m_block, batch*head). m_block varies fastest, so CTAs that run
-// together share one head's K/V in L2 (flash_attention_defs.jl:80-82). Causal
-// items differ in length (2*m_block + 2 key tiles): within a head the longest come
-// first, and since the CTA count is not a multiple of the blocks per head, the
-// round-robin hands every CTA a mix of lengths. (Sorting all items by length
-// instead spread 148 different heads over the SMs at once and measured 5-8 %
-// slower: every CTA then streams its own K/V from HBM.)
+// The work items of one CTA, in order. An item is (m_block, batch*head): 256 query
+// rows of one head.
+//  * Non-causal: item w = blockIdx.x + i * gridDim.x with m_block varying fastest, so
+//    CTAs that run together share one head's K/V in L2
+//    (flash_attention_defs.jl:80-82); all items are equally long.
+//  * Causal: item m_block visits 2*m_block + 2 key tiles. A CTA takes PAIRS of items of
+//    one head -- block n-1-t and then block t -- so every pair is 2n + 2 tiles long
+//    whatever t is: the CTAs stay in step without any sorting, the ceil(n/2) CTAs that
+//    share a head work on it at the same time, and the heads in flight (about
+//    2 * 148 / n of them) keep their K/V in L2 until all their pairs are done. (Handing
+//    out single items longest-first within a head balanced the load as well but let
+//    the 32 items of a head drift apart in time: at S = 8192 the kernel then read
+//    K and V 4.9 times from HBM. Sorting all items by length was slower still.)
 template <bool kCausal>
-__device__ __forceinline__ void decode_item(const FaParams& p, int w, int& mb, int& bh) {
-  if (kCausal) {
-    bh = w / p.num_mblocks;
-    mb = p.num_mblocks - 1 - (w % p.num_mblocks);
-  } else {
-    mb = w % p.num_mblocks;
-    bh = w / p.num_mblocks;
+struct ItemIter {
+  int v = 0;   // items this CTA has taken so far
+  __device__ __forceinline__ bool next(const FaParams& p, int& mb, int& bh) {
+    if (!kCausal) {
+      const int w = blockIdx.x + v * gridDim.x;
+      if (w >= p.total_work) return false;
+      ++v;
+      mb = w % p.num_mblocks;
+      bh = w / p.num_mblocks;
+      return true;
+    }
+    const int pairs_per_head = (p.num_mblocks + 1) >> 1;
+    while (true) {
+      const int q = blockIdx.x + (v >> 1) * gridDim.x;
+      if (q >= p.bh * pairs_per_head) return false;
+      bh = q / pairs_per_head;
+      const int t = q - bh * pairs_per_head;
+      const int far = p.num_mblocks - 1 - t;
+      const bool second = (v & 1) != 0;
+      ++v;
+      if (!second) { mb = far; return true; }
+      if (t != far) { mb = t; return true; }
+      // the middle block of an odd count has no partner: on to the next pair
+    }
   }
-}
+  // true while the item just returned by next() is this CTA's first
+  __device__ __forceinline__ bool on_first() const { return v == 1; }
+};
 // Key tiles each stage of the item visits.
 template <bool kCausal>
 __device__ __forceinline__ void tile_counts(const FaParams& p, int mb, int& nt0, int& nt1) {
@@ -290,9 +315,9 @@ __device__ __forceinline__ void fa_mma_role(const FaParams& p, uint32_t base, ui
     kv_count += n;
     if (slot >= (uint32_t)kSlots) { slot -= kSlots; ring_ph ^= 1u; }
   };
-  for (int w = blockIdx.x; w < p.total_work; w += gridDim.x, ++item_i) {
-    int mb, bh, nt[2];
-    decode_item<kCausal>(p, w, mb, bh);
+  ItemIter<kCausal> items;
+  for (int mb, bh; items.next(p, mb, bh); ++item_i) {
+    int nt[2];
     tile_counts<kCausal>(p, mb, nt[0], nt[1]);
     const int nt_max = nt[1];
     const uint32_t qph = item_i & 1u;
@@ -389,9 +414,9 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
           T::load(kv_smem + s * T::kTileBytes, tmap, row, bar(C::kBarKvFull + s));
           ++kv_it;
         };
-        for (int w = blockIdx.x; w < p.total_work; w += gridDim.x, ++item_i) {
-          int mb, bh, nt0, nt1;
-          decode_item<kCausal>(p, w, mb, bh);
+        ItemIter<kCausal> items;
+        for (int mb, bh; items.next(p, mb, bh); ++item_i) {
+          int nt0, nt1;
           tile_counts<kCausal>(p, mb, nt0, nt1);
           // grouped heads: query head h reads key/value head h / (heads_q / heads_kv)
           const int b_idx = bh / p.heads_q;
@@ -406,9 +431,9 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
           mbar_arrive_expect_tx(bar(C::kBarQFull + 1), T::kTileBytes);
           T::load(q_smem + T::kTileBytes, &tmap_q, q_row0 + kAttnRows, bar(C::kBarQFull + 1));
           for (int j = 0; j < nt1; ++j) {
-            FA_TSTAMP(w == 0, 3, j, 0);
+            FA_TSTAMP(blockIdx.x == 0 && items.on_first(), 3, j, 0);
             kv_load(&tmap_v, kv_row0 + j * kAttnRows);
-            FA_TSTAMP(w == 0, 3, j, 1);
+            FA_TSTAMP(blockIdx.x == 0 && items.on_first(), 3, j, 1);
             if (j + 1 < nt1) kv_load(&tmap_k, kv_row0 + (j + 1) * kAttnRows);
           }
         }
@@ -432,26 +457,27 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
     const uint32_t t_row = tmem_addr(tmem, (warp & 3) * 32, C::kColS + stage * 128);
     const float scale_log2 = p.scale_log2;
     uint32_t cnt_s = 0;
-    for (int w = blockIdx.x; w < p.total_work; w += gridDim.x) {
-      int mb, bh, nt[2];
-      decode_item<kCausal>(p, w, mb, bh);
+    ItemIter<kCausal> items;
+    for (int mb, bh; items.next(p, mb, bh);) {
+      int nt[2];
       tile_counts<kCausal>(p, mb, nt[0], nt[1]);
       const int ntiles = nt[stage];
+      [[maybe_unused]] const bool stamp = blockIdx.x == 0 && items.on_first() && row == 0;
       float m_run = -INFINITY;
       float l_run = 0.0f;
 #pragma unroll 1
       for (int j = 0; j < ntiles; ++j) {
-        FA_TSTAMP(w == 0 && row == 0, stage, j, 0);
+        FA_TSTAMP(stamp, stage, j, 0);
         mbar_wait(bar(C::kBarSFull + stage), cnt_s & 1u, wctx, kSiteSoftmaxSFull);
         ++cnt_s;
         tc_fence_after();
-        FA_TSTAMP(w == 0 && row == 0, stage, j, 1);
+        FA_TSTAMP(stamp, stage, j, 1);
         uint32_t v[4][32];
 #pragma unroll
         for (int c = 0; c < 4; ++c) tmem_ld32(t_row + c * 32, v[c]);
 #pragma unroll
         for (int c = 0; c < 4; ++c) tc_wait_ld_bind(v[c]);
-        FA_TSTAMP(w == 0 && row == 0, stage, j, 2);
+        FA_TSTAMP(stamp, stage, j, 2);
 
         if (kCausal && j == ntiles - 1) {
           // diagonal tile: key (local) column i is kept iff i <= row
@@ -490,7 +516,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
         stats_neg[stage * 128 + row] = neg;
         mbar_arrive(bar(C::kBarAlpha + stage));
 
-        FA_TSTAMP(w == 0 && row == 0, stage, j, 3);
+        FA_TSTAMP(stamp, stage, j, 3);
         const float2 scale2 = make_float2(scale_log2, scale_log2);
         const float2 neg2 = make_float2(neg, neg);
         float2 sum2[2] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)};
@@ -528,7 +554,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
             tc_wait_st();
             tc_fence_before();
             mbar_arrive(bar(C::kBarPFull + 2 * stage + (c >> 1)));
-            FA_TSTAMP(w == 0 && row == 0, stage, j, 4 + (c >> 1));
+            FA_TSTAMP(stamp, stage, j, 4 + (c >> 1));
           }
         }
         l_run += (sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y);
@@ -552,9 +578,9 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
     uint32_t cnt_a[2] = {0, 0};
     uint32_t cnt_h[2] = {0, 0};   // S tiles seen per stage
     uint32_t item_i = 0;
-    for (int w = blockIdx.x; w < p.total_work; w += gridDim.x, ++item_i) {
-      int mb, bh, nt[2];
-      decode_item<kCausal>(p, w, mb, bh);
+    ItemIter<kCausal> items;
+    for (int mb, bh; items.next(p, mb, bh); ++item_i) {
+      int nt[2];
       tile_counts<kCausal>(p, mb, nt[0], nt[1]);
       const int nt_max = nt[1];
       float l_part[2] = {0.0f, 0.0f};   // row sums of the columns this thread exponentiates
@@ -691,7 +717,8 @@ int launch_variant(const DeviceCtx& ctx, const CUtensorMap& tq, const CUtensorMa
                                           C::kSmemBytes));
     attr_done[ctx.device & 63] = true;
   }
-  const int grid = p.total_work < ctx.sm_count ? p.total_work : ctx.sm_count;
+  const int units = kCausal ? p.bh * ((p.num_mblocks + 1) / 2) : p.total_work;   // what ItemIter deals out
+  const int grid = units < ctx.sm_count ? units : ctx.sm_count;
   fa_fwd_kernel<D, kCausal><<<grid, kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, p);
   PTXB200_CUDA_TRY(cudaGetLastError());
   return PTXB200_OK;
@@ -857,7 +884,8 @@ extern "C" int fa_fwd_bf16_noalloc(void* O, const void* Q, const void* K, const 
   p.lse = nullptr;
   p.heads_q = H;
   p.heads_kv = H;
-  const int grid = p.total_work < nd.sm_count ? p.total_work : nd.sm_count;
+  const int units = causal ? p.bh * ((p.num_mblocks + 1) / 2) : p.total_work;
+  const int grid = units < nd.sm_count ? units : nd.sm_count;
   if (grid > kNoAllocMaxCtas) {
     set_error_text("fa_fwd_bf16_noalloc: launch needs more CTAs than the 240 flag slots of the "
                    "static scratch array");
