@@ -150,6 +150,7 @@ struct FaParams {
   float* lse;           // optional: log-sum-exp of the scaled scores per query row
   int heads_q;          // query heads per batch entry
   int heads_kv;         // key/value heads per batch entry (divides heads_q)
+  int pair_mode;        // causal only: items are dealt out in pairs (see ItemIter)
 };
 
 // The work items of one CTA, in order. An item is (m_block, batch*head): 256 query
@@ -162,19 +163,24 @@ struct FaParams {
 //    whatever t is: the CTAs stay in step without any sorting, the ceil(n/2) CTAs that
 //    share a head work on it at the same time, and the heads in flight (about
 //    2 * 148 / n of them) keep their K/V in L2 until all their pairs are done. (Handing
-//    out single items longest-first within a head balanced the load as well but let
-//    the 32 items of a head drift apart in time: at S = 8192 the kernel then read
-//    K and V 4.9 times from HBM. Sorting all items by length was slower still.)
+//    out single items longest-first within a head balances the load as well but lets
+//    the items of a head drift apart in time: at S = 8192 the kernel then read K and V
+//    4.9 times from HBM. Sorting all items by length was slower still.) A pair is a
+//    coarse unit when a launch has few of them; the host compares the two static
+//    schedules' longest CTA and falls back to single items where pairs lose more than
+//    a tenth (causal_pair_mode below).
 template <bool kCausal>
 struct ItemIter {
   int v = 0;   // items this CTA has taken so far
   __device__ __forceinline__ bool next(const FaParams& p, int& mb, int& bh) {
-    if (!kCausal) {
+    if (!kCausal || !p.pair_mode) {
       const int w = blockIdx.x + v * gridDim.x;
       if (w >= p.total_work) return false;
       ++v;
-      mb = w % p.num_mblocks;
       bh = w / p.num_mblocks;
+      // causal without pairing (small launches, where a pair is too coarse a unit):
+      // longest blocks of a head first
+      mb = kCausal ? p.num_mblocks - 1 - (w % p.num_mblocks) : w % p.num_mblocks;
       return true;
     }
     const int pairs_per_head = (p.num_mblocks + 1) >> 1;
@@ -706,6 +712,37 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
   }
 }
 
+// Longest per-CTA tile count of the two static causal schedules; pairs unless they
+// are more than a tenth longer.
+int causal_pair_mode(int bh, int nmb, int nt_all, int sm_count) {
+  const long long items = (long long)bh * nmb;
+  const int pairs_per_head = (nmb + 1) / 2;
+  const long long pairs = (long long)bh * pairs_per_head;
+  if (items > (1 << 20)) return 1;   // enough work for either; skip the simulation
+  // key tiles of block mb over both stages (tile_counts)
+  auto len = [&](int mb) {
+    const int nt0 = 2 * mb + 1 < nt_all ? 2 * mb + 1 : nt_all, nt1 = 2 * mb + 2 < nt_all ? 2 * mb + 2 : nt_all;
+    return (long long)(nt0 + nt1);
+  };
+  const int grid_i = items < sm_count ? (int)items : sm_count;
+  const int grid_p = pairs < sm_count ? (int)pairs : sm_count;
+  long long worst_i = 0, worst_p = 0;
+  for (int c = 0; c < grid_i; ++c) {
+    long long sum = 0;
+    for (long long w = c; w < items; w += grid_i) sum += len(nmb - 1 - (int)(w % nmb));
+    worst_i = sum > worst_i ? sum : worst_i;
+  }
+  for (int c = 0; c < grid_p; ++c) {
+    long long sum = 0;
+    for (long long q = c; q < pairs; q += grid_p) {
+      const int t = (int)(q % pairs_per_head), far = nmb - 1 - t;
+      sum += len(far) + (t != far ? len(t) : 0);
+    }
+    worst_p = sum > worst_p ? sum : worst_p;
+  }
+  return worst_p * 10 <= worst_i * 11 ? 1 : 0;
+}
+
 template <int D, bool kCausal>
 int launch_variant(const DeviceCtx& ctx, const CUtensorMap& tq, const CUtensorMap& tk,
                    const CUtensorMap& tv, const FaParams& p, cudaStream_t stream) {
@@ -717,7 +754,7 @@ int launch_variant(const DeviceCtx& ctx, const CUtensorMap& tq, const CUtensorMa
                                           C::kSmemBytes));
     attr_done[ctx.device & 63] = true;
   }
-  const int units = kCausal ? p.bh * ((p.num_mblocks + 1) / 2) : p.total_work;   // what ItemIter deals out
+  const int units = (kCausal && p.pair_mode) ? p.bh * ((p.num_mblocks + 1) / 2) : p.total_work;   // what ItemIter deals out
   const int grid = units < ctx.sm_count ? units : ctx.sm_count;
   fa_fwd_kernel<D, kCausal><<<grid, kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, p);
   PTXB200_CUDA_TRY(cudaGetLastError());
@@ -750,6 +787,7 @@ int launch_fa_fwd(const DeviceCtx& ctx, void* O, void* lse, const void* Q, const
   p.lse = reinterpret_cast<float*>(lse);
   p.heads_q = H;
   p.heads_kv = H_kv;
+  p.pair_mode = causal ? causal_pair_mode(p.bh, p.num_mblocks, S / kAttnRows, ctx.sm_count) : 0;
   if (D == 128) {
     return causal ? launch_variant<128, true>(ctx, tq, tk, tv, p, stream)
                   : launch_variant<128, false>(ctx, tq, tk, tv, p, stream);
@@ -884,7 +922,8 @@ extern "C" int fa_fwd_bf16_noalloc(void* O, const void* Q, const void* K, const 
   p.lse = nullptr;
   p.heads_q = H;
   p.heads_kv = H;
-  const int units = causal ? p.bh * ((p.num_mblocks + 1) / 2) : p.total_work;
+  p.pair_mode = causal ? causal_pair_mode(p.bh, p.num_mblocks, S / kAttnRows, nd.sm_count) : 0;
+  const int units = (causal && p.pair_mode) ? p.bh * ((p.num_mblocks + 1) / 2) : p.total_work;
   const int grid = units < nd.sm_count ? units : nd.sm_count;
   if (grid > kNoAllocMaxCtas) {
     set_error_text("fa_fwd_bf16_noalloc: launch needs more CTAs than the 240 flag slots of the "
