@@ -45,11 +45,12 @@ GEMM_WORKLOADS = {"c5": (8192, 8192, 8192, 20260005)}   # M, N (per GPU), K, see
 ROWWISE_WORKLOADS = {"softmax": (65536, 4096, 20260011), "rms_norm": (65536, 4096, 20260012),
                      "layer_norm": (65536, 4096, 20260013), "swiglu": (65536, 4096, 20260014)}
 # DRAM traffic of one launch (dram__bytes_read.sum + dram__bytes_write.sum) from the
-# ncu captures summarised in profiles/fa_fwd_d128_c2.md and profiles/gemm_bf16_c5.md;
-# None where no capture was taken.
+# ncu captures summarised in profiles/fa_fwd_d128_c2.md, profiles/fa_fwd_c3_c4.md and
+# profiles/gemm_bf16_c5.md.
 # (softmax: captured at rows = 16384 and scaled by 4 to the bench's 65536 rows, every row being
 # read and written once: profiles/rowwise_softmax_n4096.md)
-NCU_TRAFFIC_BYTES = {"c2": 201.38e6 + 42.33e6, "c3": None, "c4": None, "c5": 1067.3e6 + 131.1e6,
+NCU_TRAFFIC_BYTES = {"c2": 201.38e6 + 42.33e6, "c3": 201.38e6 + 45.59e6, "c4": 1646.97e6 + 519.15e6,
+                     "c5": 1067.3e6 + 131.1e6,
                      "softmax": 4 * (268.45e6 + 218.52e6)}
 FALLBACK_PEAK_TFLOPS = 1590.0
 FALLBACK_PEAK_GBS = 6650.0
