@@ -51,6 +51,8 @@ extern "C" {
 
 /* fa_fwd_bf16 flags */
 #define PTXB200_FA_NO_LAZY_RESCALE 0x1u /* rescale O on every row-max increase (no 2^8 slack) */
+#define PTXB200_FA_SINGLE_BLOCKS 0x2u   /* causal: hand out single 256-row blocks, longest first, instead
+                                           of equal-length pairs of blocks (same results bit for bit) */
 
 /* Library version: major*10000 + minor*100 + patch. */
 int ptxb200_version(void);

@@ -230,7 +230,7 @@ int fa_fwd_bf16_ex(void* O, void* lse, const void* Q, const void* K, const void*
   if (O == nullptr || Q == nullptr || K == nullptr || V == nullptr) return PTXB200_E_INVALID;
   if (B <= 0 || H <= 0 || H_kv <= 0 || S <= 0 || D <= 0) return PTXB200_E_INVALID;
   if (causal != 0 && causal != 1) return PTXB200_E_INVALID;
-  if (flags & ~PTXB200_FA_NO_LAZY_RESCALE) return PTXB200_E_INVALID;
+  if (flags & ~(PTXB200_FA_NO_LAZY_RESCALE | PTXB200_FA_SINGLE_BLOCKS)) return PTXB200_E_INVALID;
   if (!(sm_scale > 0.0f) || !(sm_scale < 1e30f)) return PTXB200_E_INVALID;
   if ((D != 64 && D != 128) || S % 128 != 0 || H % H_kv != 0) return PTXB200_E_SHAPE;
   if ((long long)B * H * S >= (1ll << 31)) return PTXB200_E_SHAPE;

@@ -787,7 +787,8 @@ int launch_fa_fwd(const DeviceCtx& ctx, void* O, void* lse, const void* Q, const
   p.lse = reinterpret_cast<float*>(lse);
   p.heads_q = H;
   p.heads_kv = H_kv;
-  p.pair_mode = causal ? causal_pair_mode(p.bh, p.num_mblocks, S / kAttnRows, ctx.sm_count) : 0;
+  p.pair_mode = (causal && !(flags & PTXB200_FA_SINGLE_BLOCKS))
+                    ? causal_pair_mode(p.bh, p.num_mblocks, S / kAttnRows, ctx.sm_count) : 0;
   if (D == 128) {
     return causal ? launch_variant<128, true>(ctx, tq, tk, tv, p, stream)
                   : launch_variant<128, false>(ctx, tq, tk, tv, p, stream);
@@ -867,7 +868,7 @@ extern "C" int fa_fwd_bf16_noalloc(void* O, const void* Q, const void* K, const 
   if (O == nullptr || Q == nullptr || K == nullptr || V == nullptr) return PTXB200_E_INVALID;
   if (B <= 0 || H <= 0 || S <= 0 || D <= 0) return PTXB200_E_INVALID;
   if (causal != 0 && causal != 1) return PTXB200_E_INVALID;
-  if (flags & ~PTXB200_FA_NO_LAZY_RESCALE) return PTXB200_E_INVALID;
+  if (flags & ~(PTXB200_FA_NO_LAZY_RESCALE | PTXB200_FA_SINGLE_BLOCKS)) return PTXB200_E_INVALID;
   if (!(sm_scale > 0.0f) || !(sm_scale < 1e30f)) return PTXB200_E_INVALID;
   if ((D != 64 && D != 128) || S % 128 != 0) return PTXB200_E_SHAPE;
   if ((long long)B * H * S >= (1ll << 31)) return PTXB200_E_SHAPE;
@@ -922,7 +923,8 @@ extern "C" int fa_fwd_bf16_noalloc(void* O, const void* Q, const void* K, const 
   p.lse = nullptr;
   p.heads_q = H;
   p.heads_kv = H;
-  p.pair_mode = causal ? causal_pair_mode(p.bh, p.num_mblocks, S / kAttnRows, nd.sm_count) : 0;
+  p.pair_mode = (causal && !(flags & PTXB200_FA_SINGLE_BLOCKS))
+                    ? causal_pair_mode(p.bh, p.num_mblocks, S / kAttnRows, nd.sm_count) : 0;
   const int units = (causal && p.pair_mode) ? p.bh * ((p.num_mblocks + 1) / 2) : p.total_work;
   const int grid = units < nd.sm_count ? units : nd.sm_count;
   if (grid > kNoAllocMaxCtas) {

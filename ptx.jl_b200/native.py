@@ -20,6 +20,7 @@ GEMM_F32_OUT = 0x1
 GEMM_NO_SPLIT = 0x2
 GEMM_ONE_CTA = 0x4
 FA_NO_LAZY_RESCALE = 0x1
+FA_SINGLE_BLOCKS = 0x2
 
 E_INVALID, E_SHAPE, E_ALIGN, E_CUDA, E_DRIVER, E_DEVICE, E_CAPACITY = -1, -2, -3, -4, -5, -6, -7
 

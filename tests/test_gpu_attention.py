@@ -108,6 +108,27 @@ def test_full_size_properties(pkg, gpu, causal):
         assert torch.equal(o1[:, :, 0, :], v[:, :, 0, :])
 
 
+@pytest.mark.parametrize("B,H,S,D", [
+    (4, 16, 4096, 128),    # 512 pairs of 16 blocks per head on 148 CTAs
+    (16, 16, 1280, 128),   # 5 blocks per head: the middle one has no partner
+    (8, 32, 2304, 64),     # 9 blocks per head, D = 64
+    (2, 2, 1024, 128),     # fewer pairs than CTAs
+    (1, 3, 384, 64),       # S % 256 == 128: the last block has only its first stage
+])
+def test_causal_schedules_agree_bit_for_bit(pkg, gpu, B, H, S, D):
+    """Causal work is handed out either as equal-length pairs of blocks of one head
+    or as single blocks, longest first (the host picks by the longest CTA; the flag
+    forces single blocks). Which CTA computes a block changes nothing in the block's
+    arithmetic, so the outputs must be identical."""
+    q, k, v = (t.to(gpu) for t in seeded_qkv(B, H, S, D, 4242 + S, 0.7))
+    lse_a = torch.empty(B * H * S, dtype=torch.float32, device=gpu)
+    lse_b = torch.empty_like(lse_a)
+    a = pkg.ops.fa_fwd(q, k, v, causal=True, lse=lse_a)
+    b = pkg.ops.fa_fwd(q, k, v, causal=True, lse=lse_b, flags=pkg.native.FA_SINGLE_BLOCKS)
+    assert pkg.ops.sync_status() == 0
+    assert torch.equal(a, b) and torch.equal(lse_a, lse_b)
+
+
 @pytest.mark.parametrize("name,B,H,S,D,causal,sigma", [
     ("c2", 4, 16, 4096, 128, False, 1.0),
     ("c3", 16, 16, 2048, 64, False, 1.0),
