@@ -27,6 +27,7 @@
 // cluster barrier before the first remote arrival and before exit.
 //
 // Work per launch: 2*G*M*N*K flop; compulsory bytes G*((M*K + N*K)*2 + M*N*sizeof(out)).
+#include "gemm_epilogue.cuh"
 #include "host_common.h"
 #include "sm100_prims.cuh"
 
@@ -264,24 +265,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         tmem_ld32(t_row + c * 32, v);
         tc_wait_ld_bind(v);
         const int col = col0 + c * 32;
-        if (col < N && rows_valid) {
-          if (kF32Out) {
-            float* dst = reinterpret_cast<float*>(c_out) + row * (size_t)ldc + col;
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-              st_global_v4(dst + 4 * i, v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-          } else {
-            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(c_out) + row * (size_t)ldc + col;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const uint32_t p0 = pack_bf16x2(__uint_as_float(v[8 * i + 0]), __uint_as_float(v[8 * i + 1]));
-              const uint32_t p1 = pack_bf16x2(__uint_as_float(v[8 * i + 2]), __uint_as_float(v[8 * i + 3]));
-              const uint32_t p2 = pack_bf16x2(__uint_as_float(v[8 * i + 4]), __uint_as_float(v[8 * i + 5]));
-              const uint32_t p3 = pack_bf16x2(__uint_as_float(v[8 * i + 6]), __uint_as_float(v[8 * i + 7]));
-              st_global_v4(dst + 8 * i, p0, p1, p2, p3);
-            }
-          }
-        }
+        if (col < N && rows_valid) store_acc_chunk<kF32Out>(c_out, row, ldc, col, v);
       }
       tc_fence_before();
       mbar_arrive_cluster(leader_acc_empty + 8 * buf);

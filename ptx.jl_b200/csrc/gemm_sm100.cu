@@ -44,6 +44,7 @@
 #include <mutex>
 #include <utility>
 
+#include "gemm_epilogue.cuh"
 #include "host_common.h"
 #include "sm100_prims.cuh"
 
@@ -249,25 +250,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     // ---------------- epilogue: warps 2..5 ----------------
     const int quad = warp & 3;                       // TMEM lane quadrant this warp may touch
     const int row_in_tile = quad * 32 + lane;
-    // 32 accumulator columns of one row -> C
-    auto store_chunk = [&](size_t row, int col, const uint32_t (&v)[32]) {
-      if (kF32Out) {
-        float* dst = reinterpret_cast<float*>(c_out) + row * (size_t)ldc + col;
-#pragma unroll
-        for (int i = 0; i < 8; ++i)
-          st_global_v4(dst + 4 * i, v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-      } else {
-        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(c_out) + row * (size_t)ldc + col;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const uint32_t p0 = pack_bf16x2(__uint_as_float(v[8 * i + 0]), __uint_as_float(v[8 * i + 1]));
-          const uint32_t p1 = pack_bf16x2(__uint_as_float(v[8 * i + 2]), __uint_as_float(v[8 * i + 3]));
-          const uint32_t p2 = pack_bf16x2(__uint_as_float(v[8 * i + 4]), __uint_as_float(v[8 * i + 5]));
-          const uint32_t p3 = pack_bf16x2(__uint_as_float(v[8 * i + 6]), __uint_as_float(v[8 * i + 7]));
-          st_global_v4(dst + 8 * i, p0, p1, p2, p3);
-        }
-      }
-    };
     uint32_t t = 0;
     UnitIter units;
     units.init(sched);
@@ -291,7 +273,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           tmem_ld32(t_row + c * 32, v);
           tc_wait_ld_bind(v);
           const int col = col0 + c * 32;
-          if (col < N) store_chunk(row, col, v);
+          if (col < N) store_acc_chunk<kF32Out>(c_out, row, ldc, col, v);
         }
         // every TMEM read of this accumulator has completed (wait::ld above)
         tc_fence_before();
