@@ -144,8 +144,11 @@ int swiglu_f32(void* out, const void* gate, const void* up, long long n, void* s
  *   Q, K, V, O  [B,H,S,D] row-major bf16 == a 2-D (B*H*S, D) matrix, D contiguous
  *               (the reference's layout: flash_attention_defs.jl:90, 979-986)
  *   D           64 or 128
- *   S           multiple of 128 (work is cut in 256-row items; an odd number of
- *               128-row blocks leaves the last item of each head half empty)
+ *   S           any length >= 1 (work is cut in 256-row items of 128-key tiles; rows
+ *               and keys past the end of a sequence are loaded as zeros through
+ *               per-head tensor maps, masked out of the softmax and not written.
+ *               The reference asserts S % 256 == 0 and more:
+ *               bench/flash_attention.jl:43-47)
  *   causal      0: every key; 1: key j is kept for query i iff j <= i
  *               (mask convention of test/gpu/ampere/flash_attention.jl:176-186)
  *   dbg         NULL, or 64 uint32 words on the device that receive per-role
@@ -200,6 +203,8 @@ int fa_fwd_bf16_ex(void* O, void* lse, const void* Q, const void* K, const void*
  * fa_fwd_bf16 (same kernel code); there is no dbg argument.
  *
  * Limits and rules
+ *   - Non-causal calls need S % 128 == 0 here (PTXB200_E_SHAPE otherwise); fa_fwd_bf16
+ *     takes any S.
  *   - Capacity: at most 240 CTAs (one per SM) and device ordinals 0..63; beyond
  *     that the call returns PTXB200_E_CAPACITY and launches nothing.
  *   - The first call on each device looks up the array's device address and sets

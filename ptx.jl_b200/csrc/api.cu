@@ -105,6 +105,27 @@ int encode_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t rows, uint6
   return PTXB200_OK;
 }
 
+int encode_tmap_bf16_3d(CUtensorMap* out, const void* base, uint64_t slices, uint64_t rows, uint64_t cols,
+                        uint32_t box_rows, uint32_t box_cols) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) {
+    set_error_text("cuTensorMapEncodeTiled: driver entry point not found");
+    return PTXB200_E_DRIVER;
+  }
+  cuuint64_t dims[3] = {cols, rows, slices};                       // innermost first
+  cuuint64_t strides[2] = {cols * 2, rows * cols * 2};             // bytes, of dims 1 and 2
+  cuuint32_t box[3] = {box_cols, box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    snprintf(g_err, sizeof(g_err), "cuTensorMapEncodeTiled (3-D) failed with CUresult %d", (int)r);
+    return PTXB200_E_DRIVER;
+  }
+  return PTXB200_OK;
+}
+
 }  // namespace ptxb200
 
 using namespace ptxb200;
@@ -232,7 +253,7 @@ int fa_fwd_bf16_ex(void* O, void* lse, const void* Q, const void* K, const void*
   if (causal != 0 && causal != 1) return PTXB200_E_INVALID;
   if (flags & ~(PTXB200_FA_NO_LAZY_RESCALE | PTXB200_FA_SINGLE_BLOCKS)) return PTXB200_E_INVALID;
   if (!(sm_scale > 0.0f) || !(sm_scale < 1e30f)) return PTXB200_E_INVALID;
-  if ((D != 64 && D != 128) || S % 128 != 0 || H % H_kv != 0) return PTXB200_E_SHAPE;
+  if ((D != 64 && D != 128) || H % H_kv != 0) return PTXB200_E_SHAPE;
   if ((long long)B * H * S >= (1ll << 31)) return PTXB200_E_SHAPE;
   if (!aligned16(O) || !aligned16(Q) || !aligned16(K) || !aligned16(V)) return PTXB200_E_ALIGN;
   if ((dbg != nullptr && !aligned16(dbg)) || (lse != nullptr && !aligned16(lse))) return PTXB200_E_ALIGN;

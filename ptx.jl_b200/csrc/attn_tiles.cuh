@@ -60,6 +60,14 @@ struct AttnTile {
     for (int s = 0; s < kStripes; ++s)
       tma_load_2d(dst_smem + s * kStripeBytes, tmap, s * 64, row, bar);
   }
+  // The same from a 3-D map (slice = batch*head): rows past the end of the slice's
+  // sequence come in as zeros.
+  static __device__ __forceinline__ void load3(uint32_t dst_smem, const void* tmap, int row, int slice,
+                                               uint32_t bar) {
+#pragma unroll
+    for (int s = 0; s < kStripes; ++s)
+      tma_load_3d(dst_smem + s * kStripeBytes, tmap, s * 64, row, slice, bar);
+  }
 #endif
 };
 

@@ -200,15 +200,17 @@ struct ItemIter {
   // true while the item just returned by next() is this CTA's first
   __device__ __forceinline__ bool on_first() const { return v == 1; }
 };
+template <bool V> struct BoolTag { static constexpr bool value = V; };
+
 // Key tiles each stage of the item visits.
 template <bool kCausal>
 __device__ __forceinline__ void tile_counts(const FaParams& p, int mb, int& nt0, int& nt1) {
+  const int nt_all = (p.seqlen + kAttnRows - 1) / kAttnRows;   // the last tile may be partly past the end
   if (kCausal) {
-    const int nt_all = p.seqlen / kAttnRows;
     nt0 = min(2 * mb + 1, nt_all);
     nt1 = min(2 * mb + 2, nt_all);   // equals nt0 in a last block that has only its first stage
   } else {
-    nt0 = nt1 = p.seqlen / kAttnRows;
+    nt0 = nt1 = nt_all;
   }
 }
 
@@ -344,7 +346,10 @@ __device__ __forceinline__ void fa_mma_role(const FaParams& p, uint32_t base, ui
 // kCtaFlags: additionally mark, in p.cta_flags[blockIdx.x], every CTA in which a
 // bounded wait ran out (used by the entry point that keeps its scratch in a static
 // device array).
-template <int D, bool kCausal, bool kCtaFlags = false>
+// kRagged (non-causal only): the sequence length is not a multiple of 128, so the last key
+// tile holds keys past the end that must be masked. A variant of its own because the
+// masking code, though it runs once per item, costs the common case 1-2 % when compiled in.
+template <int D, bool kCausal, bool kCtaFlags = false, bool kRagged = false>
 __global__ void __launch_bounds__(kThreads, 1)
 fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
               const __grid_constant__ CUtensorMap tmap_v, const FaParams p) {
@@ -412,12 +417,12 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
         tma_prefetch_desc(&tmap_k);
         tma_prefetch_desc(&tmap_v);
         uint32_t kv_it = 0, item_i = 0;
-        auto kv_load = [&](const void* tmap, int row) {
+        auto kv_load = [&](const void* tmap, int row, int slice) {
           const uint32_t s = kv_it % C::kSlots;
           const uint32_t ph = (kv_it / C::kSlots) & 1u;
           mbar_wait(bar(C::kBarKvFree + s), ph ^ 1u, wctx, kSiteLoadKvFree);
           mbar_arrive_expect_tx(bar(C::kBarKvFull + s), T::kTileBytes);
-          T::load(kv_smem + s * T::kTileBytes, tmap, row, bar(C::kBarKvFull + s));
+          T::load3(kv_smem + s * T::kTileBytes, tmap, row, slice, bar(C::kBarKvFull + s));
           ++kv_it;
         };
         ItemIter<kCausal> items;
@@ -427,20 +432,20 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
           // grouped heads: query head h reads key/value head h / (heads_q / heads_kv)
           const int b_idx = bh / p.heads_q;
           const int kv_head = (bh - b_idx * p.heads_q) / (p.heads_q / p.heads_kv);
-          const int kv_row0 = (b_idx * p.heads_kv + kv_head) * p.seqlen;
-          const int q_row0 = bh * p.seqlen + mb * 2 * kAttnRows;
+          const int kv_slice = b_idx * p.heads_kv + kv_head;
+          const int q_row0 = mb * 2 * kAttnRows;   // within the head's sequence; rows past its end load as zeros
           // Q may be overwritten once every S = Q K^T of the previous item has run
           mbar_wait(bar(C::kBarQFree), (item_i & 1u) ^ 1u, wctx, kSiteLoadQFree);
           mbar_arrive_expect_tx(bar(C::kBarQFull + 0), T::kTileBytes);
-          T::load(q_smem, &tmap_q, q_row0, bar(C::kBarQFull + 0));
-          kv_load(&tmap_k, kv_row0);
+          T::load3(q_smem, &tmap_q, q_row0, bh, bar(C::kBarQFull + 0));
+          kv_load(&tmap_k, 0, kv_slice);
           mbar_arrive_expect_tx(bar(C::kBarQFull + 1), T::kTileBytes);
-          T::load(q_smem + T::kTileBytes, &tmap_q, q_row0 + kAttnRows, bar(C::kBarQFull + 1));
+          T::load3(q_smem + T::kTileBytes, &tmap_q, q_row0 + kAttnRows, bh, bar(C::kBarQFull + 1));
           for (int j = 0; j < nt1; ++j) {
             FA_TSTAMP(blockIdx.x == 0 && items.on_first(), 3, j, 0);
-            kv_load(&tmap_v, kv_row0 + j * kAttnRows);
+            kv_load(&tmap_v, j * kAttnRows, kv_slice);
             FA_TSTAMP(blockIdx.x == 0 && items.on_first(), 3, j, 1);
-            if (j + 1 < nt1) kv_load(&tmap_k, kv_row0 + (j + 1) * kAttnRows);
+            if (j + 1 < nt1) kv_load(&tmap_k, (j + 1) * kAttnRows, kv_slice);
           }
         }
         if (p.dbg != nullptr && blockIdx.x == 0) p.dbg[0] = kv_it;
@@ -468,6 +473,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
       int nt[2];
       tile_counts<kCausal>(p, mb, nt[0], nt[1]);
       const int ntiles = nt[stage];
+      [[maybe_unused]] const int kv_tail = p.seqlen - (ntiles - 1) * kAttnRows;   // keys in the last tile (non-causal)
       [[maybe_unused]] const bool stamp = blockIdx.x == 0 && items.on_first() && row == 0;
       float m_run = -INFINITY;
       float l_run = 0.0f;
@@ -486,12 +492,22 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
         FA_TSTAMP(stamp, stage, j, 2);
 
         if (kCausal && j == ntiles - 1) {
-          // diagonal tile: key (local) column i is kept iff i <= row
+          // diagonal tile: key (local) column i is kept iff i <= row (keys past the end of
+          // the sequence lie beyond every valid row's diagonal)
 #pragma unroll
           for (int c = 0; c < 4; ++c)
 #pragma unroll
             for (int i = 0; i < 32; ++i)
               if (c * 32 + i > row) v[c][i] = 0xFF800000u;  // -inf
+        }
+        if (kRagged && !kCausal && j == ntiles - 1 && kv_tail < kAttnRows) {
+          // last tile of a sequence that is not a multiple of 128: its keys past the end
+          // loaded as zeros and must not count
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (c * 32 + i >= kv_tail) v[c][i] = 0xFF800000u;  // -inf
         }
 
         float mx[4];
@@ -597,7 +613,11 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
         for (int s = 0; s < 2; ++s) {
           if (j < nt[s]) {
             uint32_t sv[32];
-            [[maybe_unused]] const bool diag = kCausal && j == nt[s] - 1;
+            // Only a stage's last tile can hold masked keys: those above the diagonal
+            // (causal) or past the end of the sequence (non-causal, S % 128 != 0). `keep`
+            // is the last key column this row keeps there.
+            const bool mask_tile = j == nt[s] - 1 && (kCausal || (kRagged && p.seqlen - j * kAttnRows < kAttnRows));
+            const int keep = kCausal ? row : p.seqlen - j * kAttnRows - 1;
             {
               // fetch this row's last 32 scores while the softmax warp forms the maximum
               mbar_wait(bar(C::kBarSFull + s), cnt_h[s] & 1u, wctx, kSiteSoftmaxSFull);
@@ -635,18 +655,23 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
               const float2 neg2 = make_float2(neg, neg);
               float2 sum2 = make_float2(0.0f, 0.0f);
               uint32_t pk[16];
+              // two copies of the loop, so that the tiles without masked keys (all but one
+              // per stage) carry no per-element compares
+              auto exps = [&](auto masked) {
 #pragma unroll
-              for (int i = 0; i < 16; ++i) {
-                float2 e = exp2_poly2(__ffma2_rn(
-                    make_float2(__uint_as_float(sv[2 * i]), __uint_as_float(sv[2 * i + 1])), scale2, neg2));
-                if (kCausal) {
-                  // diagonal tile: keys above the diagonal weigh exactly zero
-                  if (diag && 96 + 2 * i > row) e.x = 0.0f;
-                  if (diag && 96 + 2 * i + 1 > row) e.y = 0.0f;
+                for (int i = 0; i < 16; ++i) {
+                  float2 e = exp2_poly2(__ffma2_rn(
+                      make_float2(__uint_as_float(sv[2 * i]), __uint_as_float(sv[2 * i + 1])), scale2, neg2));
+                  if (decltype(masked)::value) {
+                    // masked keys weigh exactly zero (the polynomial bottoms out at 2^-126)
+                    if (96 + 2 * i > keep) e.x = 0.0f;
+                    if (96 + 2 * i + 1 > keep) e.y = 0.0f;
+                  }
+                  sum2 = __fadd2_rn(sum2, e);
+                  pk[i] = pack_bf16x2(e.x, e.y);
                 }
-                sum2 = __fadd2_rn(sum2, e);
-                pk[i] = pack_bf16x2(e.x, e.y);
-              }
+              };
+              if (mask_tile) exps(BoolTag<true>{}); else exps(BoolTag<false>{});
               tmem_st16(t_lane + C::kColS + s * 128 + 48, pk);   // P columns of keys 96..127
               tc_wait_st();
               tc_fence_before();
@@ -660,18 +685,17 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
       const int q_row0 = bh * p.seqlen + mb * 2 * kAttnRows;
 #pragma unroll
       for (int s = 0; s < 2; ++s) {
+        // rows past the end of the sequence were computed on zero-filled queries: not written
+        const bool row_valid = mb * 2 * kAttnRows + s * kAttnRows + row < p.seqlen;
         mbar_wait(bar(C::kBarODone + s), item_i & 1u, wctx, kSiteCorrODone);
         mbar_wait(bar(C::kBarLReady + s), item_i & 1u, wctx, kSiteCorrLReady);
         tc_fence_after();
         const float l_total = stats_l[s * 128 + row] + l_part[s];
         const float inv_l = 1.0f / l_total;
-        if (p.lse != nullptr && mb * 2 * kAttnRows + s * kAttnRows < p.seqlen) {
+        if (p.lse != nullptr && row_valid) {
           // sum_j 2^(s_j c) = 2^(m c) * l with basis -m c in neg_prev: natural log of it
           p.lse[q_row0 + s * kAttnRows + row] = (log2f(l_total) - neg_prev[s]) * 0.6931471805599453f;
         }
-        // a sequence of an odd number of 128-row blocks ends with a half-empty item: its
-        // second stage computes on rows past the end and is simply not written out
-        const bool stage_valid = mb * 2 * kAttnRows + s * kAttnRows < p.seqlen;
         __nv_bfloat16* dst = p.o + (size_t)(q_row0 + s * kAttnRows + row) * D;
 #pragma unroll 1
         for (int c = 0; c < D / 32; ++c) {
@@ -689,7 +713,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
             const uint32_t p1 = pack_bf16x2(__uint_as_float(o[8 * i + 2]) * inv_l, __uint_as_float(o[8 * i + 3]) * inv_l);
             const uint32_t p2 = pack_bf16x2(__uint_as_float(o[8 * i + 4]) * inv_l, __uint_as_float(o[8 * i + 5]) * inv_l);
             const uint32_t p3 = pack_bf16x2(__uint_as_float(o[8 * i + 6]) * inv_l, __uint_as_float(o[8 * i + 7]) * inv_l);
-            if (stage_valid) st_global_v4(dst + c * 32 + 8 * i, p0, p1, p2, p3);
+            if (row_valid) st_global_v4(dst + c * 32 + 8 * i, p0, p1, p2, p3);
           }
         }
       }
@@ -752,11 +776,18 @@ int launch_variant(const DeviceCtx& ctx, const CUtensorMap& tq, const CUtensorMa
     PTXB200_CUDA_TRY(cudaFuncSetAttribute(fa_fwd_kernel<D, kCausal>,
                                           cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           C::kSmemBytes));
+    if (!kCausal)
+      PTXB200_CUDA_TRY(cudaFuncSetAttribute(fa_fwd_kernel<D, false, false, true>,
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            C::kSmemBytes));
     attr_done[ctx.device & 63] = true;
   }
   const int units = (kCausal && p.pair_mode) ? p.bh * ((p.num_mblocks + 1) / 2) : p.total_work;   // what ItemIter deals out
   const int grid = units < ctx.sm_count ? units : ctx.sm_count;
-  fa_fwd_kernel<D, kCausal><<<grid, kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, p);
+  if (!kCausal && p.seqlen % kAttnRows != 0)
+    fa_fwd_kernel<D, false, false, true><<<grid, kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, p);
+  else
+    fa_fwd_kernel<D, kCausal><<<grid, kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, p);
   PTXB200_CUDA_TRY(cudaGetLastError());
   return PTXB200_OK;
 }
@@ -766,13 +797,11 @@ int launch_variant(const DeviceCtx& ctx, const CUtensorMap& tq, const CUtensorMa
 int launch_fa_fwd(const DeviceCtx& ctx, void* O, void* lse, const void* Q, const void* K,
                   const void* V, int B, int H, int H_kv, int S, int D, float sm_scale, int causal,
                   unsigned flags, void* dbg, uint32_t* status, cudaStream_t stream) {
-  const uint64_t rows = (uint64_t)B * H * S;
-  const uint64_t rows_kv = (uint64_t)B * H_kv * S;
   CUtensorMap tq, tk, tv;
   int rc;
-  if ((rc = encode_tmap_bf16_2d(&tq, Q, rows, D, (uint64_t)D * 2, 128, 64)) != PTXB200_OK) return rc;
-  if ((rc = encode_tmap_bf16_2d(&tk, K, rows_kv, D, (uint64_t)D * 2, 128, 64)) != PTXB200_OK) return rc;
-  if ((rc = encode_tmap_bf16_2d(&tv, V, rows_kv, D, (uint64_t)D * 2, 128, 64)) != PTXB200_OK) return rc;
+  if ((rc = encode_tmap_bf16_3d(&tq, Q, (uint64_t)B * H, S, D, 128, 64)) != PTXB200_OK) return rc;
+  if ((rc = encode_tmap_bf16_3d(&tk, K, (uint64_t)B * H_kv, S, D, 128, 64)) != PTXB200_OK) return rc;
+  if ((rc = encode_tmap_bf16_3d(&tv, V, (uint64_t)B * H_kv, S, D, 128, 64)) != PTXB200_OK) return rc;
   FaParams p;
   p.o = reinterpret_cast<__nv_bfloat16*>(O);
   p.seqlen = S;
@@ -788,7 +817,7 @@ int launch_fa_fwd(const DeviceCtx& ctx, void* O, void* lse, const void* Q, const
   p.heads_q = H;
   p.heads_kv = H_kv;
   p.pair_mode = (causal && !(flags & PTXB200_FA_SINGLE_BLOCKS))
-                    ? causal_pair_mode(p.bh, p.num_mblocks, S / kAttnRows, ctx.sm_count) : 0;
+                    ? causal_pair_mode(p.bh, p.num_mblocks, (S + kAttnRows - 1) / kAttnRows, ctx.sm_count) : 0;
   if (D == 128) {
     return causal ? launch_variant<128, true>(ctx, tq, tk, tv, p, stream)
                   : launch_variant<128, false>(ctx, tq, tk, tv, p, stream);
@@ -870,7 +899,7 @@ extern "C" int fa_fwd_bf16_noalloc(void* O, const void* Q, const void* K, const 
   if (causal != 0 && causal != 1) return PTXB200_E_INVALID;
   if (flags & ~(PTXB200_FA_NO_LAZY_RESCALE | PTXB200_FA_SINGLE_BLOCKS)) return PTXB200_E_INVALID;
   if (!(sm_scale > 0.0f) || !(sm_scale < 1e30f)) return PTXB200_E_INVALID;
-  if ((D != 64 && D != 128) || S % 128 != 0) return PTXB200_E_SHAPE;
+  if ((D != 64 && D != 128) || (S % 128 != 0 && !causal)) return PTXB200_E_SHAPE;
   if ((long long)B * H * S >= (1ll << 31)) return PTXB200_E_SHAPE;
   if (!aligned16(O) || !aligned16(Q) || !aligned16(K) || !aligned16(V)) return PTXB200_E_ALIGN;
   cudaStream_t stream = (cudaStream_t)stream_v;
@@ -924,7 +953,7 @@ extern "C" int fa_fwd_bf16_noalloc(void* O, const void* Q, const void* K, const 
   p.heads_q = H;
   p.heads_kv = H;
   p.pair_mode = (causal && !(flags & PTXB200_FA_SINGLE_BLOCKS))
-                    ? causal_pair_mode(p.bh, p.num_mblocks, S / kAttnRows, nd.sm_count) : 0;
+                    ? causal_pair_mode(p.bh, p.num_mblocks, (S + kAttnRows - 1) / kAttnRows, nd.sm_count) : 0;
   const int units = (causal && p.pair_mode) ? p.bh * ((p.num_mblocks + 1) / 2) : p.total_work;
   const int grid = units < nd.sm_count ? units : nd.sm_count;
   if (grid > kNoAllocMaxCtas) {
@@ -933,12 +962,11 @@ extern "C" int fa_fwd_bf16_noalloc(void* O, const void* Q, const void* K, const 
     return PTXB200_E_CAPACITY;
   }
 
-  const uint64_t rows = (uint64_t)B * H * S;
   CUtensorMap tq, tk, tv;
   int rc;
-  if ((rc = encode_tmap_bf16_2d(&tq, Q, rows, D, (uint64_t)D * 2, 128, 64)) != PTXB200_OK) return rc;
-  if ((rc = encode_tmap_bf16_2d(&tk, K, rows, D, (uint64_t)D * 2, 128, 64)) != PTXB200_OK) return rc;
-  if ((rc = encode_tmap_bf16_2d(&tv, V, rows, D, (uint64_t)D * 2, 128, 64)) != PTXB200_OK) return rc;
+  if ((rc = encode_tmap_bf16_3d(&tq, Q, (uint64_t)B * H, S, D, 128, 64)) != PTXB200_OK) return rc;
+  if ((rc = encode_tmap_bf16_3d(&tk, K, (uint64_t)B * H, S, D, 128, 64)) != PTXB200_OK) return rc;
+  if ((rc = encode_tmap_bf16_3d(&tv, V, (uint64_t)B * H, S, D, 128, 64)) != PTXB200_OK) return rc;
 
   // The array keeps what the previous call left: the status word and the flags of
   // the CTAs this launch uses must start at zero.

@@ -47,6 +47,12 @@ const char* get_cuda_error();
 int encode_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols,
                         uint64_t row_pitch_bytes, uint32_t box_rows, uint32_t box_cols);
 
+// 3-D bf16 tensor map over `slices` contiguous row-major matrices of `rows` x `cols`
+// (one per batch*head), box 1 x `box_rows` x `box_cols`, 128-byte swizzle. Rows past
+// the end of a slice read as zeros instead of the next slice's rows.
+int encode_tmap_bf16_3d(CUtensorMap* out, const void* base, uint64_t slices, uint64_t rows, uint64_t cols,
+                        uint32_t box_rows, uint32_t box_cols);
+
 #define PTXB200_CUDA_TRY(expr)                         \
   do {                                                 \
     cudaError_t _e = (expr);                           \

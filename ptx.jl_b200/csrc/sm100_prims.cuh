@@ -189,6 +189,16 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const void* tmap,
       "l"((uint64_t)tmap), "r"(c0), "r"(c1), "r"(bar)
       : "memory");
 }
+// 3-D form: c0 innermost (elements, c0 * element size a multiple of 16 bytes), c1 the
+// row, c2 the slice. Coordinates past an extent read the fill value (zero).
+__device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const void* tmap, int c0, int c1, int c2,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst_smem),
+      "l"((uint64_t)tmap), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
+      : "memory");
+}
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)tmap) : "memory");
 }

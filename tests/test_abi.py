@@ -61,7 +61,7 @@ def test_host_side_argument_checks(pkg):
     assert L.gemm_bf16_grouped(p, p, p, 2, 128, 64, 64, 68, 0, None) == n.E_ALIGN
     assert L.fa_fwd_bf16(p, p, p, None, 1, 1, 256, 128, sc, 0, 0, None, None) == n.E_INVALID
     assert L.fa_fwd_bf16(p, p, p, p, 1, 1, 256, 128, ctypes.c_float(0.0), 0, 0, None, None) == n.E_INVALID
-    assert L.fa_fwd_bf16(p, p, p, p, 1, 1, 192, 128, sc, 0, 0, None, None) == n.E_SHAPE
+    assert L.fa_fwd_bf16(p, p, p, p, 1, 1, 0, 128, sc, 0, 0, None, None) == n.E_INVALID
     assert L.fa_fwd_bf16(p, p, p, p, 1, 1, 256, 32, sc, 0, 0, None, None) == n.E_SHAPE
     assert L.fa_fwd_bf16(p, p, p, p, 1 << 12, 1 << 12, 256, 128, sc, 0, 0, None, None) == n.E_SHAPE
     assert L.fa_fwd_bf16(p, p + 4, p, p, 1, 1, 256, 128, sc, 0, 0, None, None) == n.E_ALIGN

@@ -108,6 +108,33 @@ def test_full_size_properties(pkg, gpu, causal):
         assert torch.equal(o1[:, :, 0, :], v[:, :, 0, :])
 
 
+@pytest.mark.parametrize("S", [1, 7, 100, 127, 129, 200, 255, 257, 1000, 2049])
+@pytest.mark.parametrize("D", [128, 64])
+@pytest.mark.parametrize("causal", [False, True])
+def test_any_sequence_length(pkg, gpu, oracle_mod, S, D, causal):
+    """Sequence lengths that are no multiple of the 128-row tile (the reference asserts
+    S % 256 == 0): rows and keys past the end load as zeros through the per-head tensor
+    maps; the keys are masked out of the softmax, the rows are not written. The output
+    buffer is longer than needed and pre-filled, so a write past the end would show."""
+    B, H = 2, 3
+    q, k, v = seeded_qkv(B, H, S, D, 900 + S, 0.8)
+    out = torch.full((B * H * S * D + 4096,), 7.0, dtype=torch.bfloat16, device=gpu)
+    o = out[:B * H * S * D].view(B, H, S, D)
+    lse = torch.full((B * H * S + 64,), 7.0, dtype=torch.float32, device=gpu)
+    pkg.ops.fa_fwd(q.to(gpu), k.to(gpu), v.to(gpu), causal=causal, out=o, lse=lse[:B * H * S])
+    assert pkg.ops.sync_status() == 0
+    assert torch.all(out[B * H * S * D:] == 7.0) and torch.all(lse[B * H * S:] == 7.0)
+    ref = oracle_mod.attention_ref_c(bits(q).reshape(B * H, S, D), bits(k).reshape(B * H, S, D),
+                                     bits(v).reshape(B * H, S, D), 1.0 / D ** 0.5, causal)
+    mx, mean = attn_errors(o, ref)
+    assert mx <= ATTN_MAX_ABS and mean <= ATTN_MEAN_ABS, (mx, mean)
+    qf, kf = q.float().numpy().reshape(B * H, S, D), k.float().numpy().reshape(B * H, S, D)
+    got_lse = lse[:B * H * S].cpu().numpy().reshape(B * H, S)
+    for i in range(B * H):
+        np.testing.assert_allclose(got_lse[i], oracle_mod.attention_lse_numpy(qf[i], kf[i], 1.0 / D ** 0.5, causal),
+                                   atol=2e-2, rtol=1e-3)
+
+
 @pytest.mark.parametrize("B,H,S,D", [
     (4, 16, 4096, 128),    # 512 pairs of 16 blocks per head on 148 CTAs
     (16, 16, 1280, 128),   # 5 blocks per head: the middle one has no partner
@@ -198,7 +225,7 @@ def test_rejects_bad_arguments(pkg, gpu):
     P = t.data_ptr()
     import ctypes
     sc = ctypes.c_float(0.1)
-    assert L.fa_fwd_bf16(P, P, P, P, 1, 1, 200, 128, sc, 0, 0, None, None) == pkg.native.E_SHAPE
+    assert L.fa_fwd_bf16(P, P, P, P, 1, 1, 0, 128, sc, 0, 0, None, None) == pkg.native.E_INVALID
     assert L.fa_fwd_bf16(P, P, P, P, 1, 1, 256, 96, sc, 0, 0, None, None) == pkg.native.E_SHAPE
     assert L.fa_fwd_bf16(None, P, P, P, 1, 1, 256, 128, sc, 0, 0, None, None) == pkg.native.E_INVALID
     assert L.fa_fwd_bf16(P, P + 2, P, P, 1, 1, 256, 128, sc, 0, 0, None, None) == pkg.native.E_ALIGN

@@ -56,6 +56,6 @@ def test_noalloc_rejects_bad_arguments(pkg, gpu):
     t = torch.zeros(1, 1, 256, 128, dtype=torch.bfloat16, device=gpu)
     L, n, P = pkg.native.lib(), pkg.native, t.data_ptr()
     sc = ctypes.c_float(0.1)
-    assert L.fa_fwd_bf16_noalloc(P, P, P, P, 1, 1, 200, 128, sc, 0, 0, None) == n.E_SHAPE
+    assert L.fa_fwd_bf16_noalloc(P, P, P, P, 1, 1, 256, 96, sc, 0, 0, None) == n.E_SHAPE
     assert L.fa_fwd_bf16_noalloc(None, P, P, P, 1, 1, 256, 128, sc, 0, 0, None) == n.E_INVALID
     assert L.fa_fwd_bf16_noalloc(P, P + 2, P, P, 1, 1, 256, 128, sc, 0, 0, None) == n.E_ALIGN
