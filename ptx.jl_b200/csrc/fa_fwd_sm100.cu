@@ -30,13 +30,13 @@
 // warp 12 MMA issue, warp 13 TMA loads, warps 14-15 idle (they only take part in
 // the register re-split).
 //
-// Barriers: q_full[2], q_free, kv_full[n], kv_free[n] (TMA ring); s_full[2] (MMA ->
+// Barriers: q_full[2], q_free[2], kv_full[n], kv_free[n] (TMA ring); s_full[2] (MMA ->
 // softmax and correction warps); basis[2] (softmax -> correction, every tile: the
 // row's basis -m*c, from whose change the O rescale factor follows);
 // p_full[stage][half]: half 0 completes with 128 softmax arrivals (P columns 0-31
 // stored) plus 128 correction arrivals (O rescaled for this tile, or free after the
 // previous item's epilogue), half 1 with 128 softmax arrivals (columns 32-47) plus
-// 128 correction arrivals (columns 48-63); l_ready[2], o_done[2] (end of item).
+// 128 correction arrivals (columns 48-63); l_ready[2], o_done[2], l_free[2] (end of item).
 //
 // Tensor memory (512 columns x 128 lanes of 32 bit):
 //   S0 at 0, S1 at 128 (fp32, 128 columns each; P_s overwrites the first 64
@@ -119,15 +119,16 @@ struct FaCfg {
   static constexpr int kOffBars = kOffStats + 4 * 128 * 4;   // basis[2][128], l[2][128]
   // barrier indices (8 bytes each)
   static constexpr int kBarQFull = 0;                  // [2]  TMA tx
-  static constexpr int kBarQFree = 2;                  //      tcgen05.commit
-  static constexpr int kBarKvFull = 3;                 // [kSlots] TMA tx
+  static constexpr int kBarQFree = 2;                  // [2]  tcgen05.commit behind a stage's last Q K^T of an item
+  static constexpr int kBarKvFull = 4;                 // [kSlots] TMA tx
   static constexpr int kBarKvFree = kBarKvFull + kSlots;   // [kSlots] tcgen05.commit
   static constexpr int kBarSFull = kBarKvFree + kSlots;    // [2] tcgen05.commit
   static constexpr int kBarPFull = kBarSFull + 2;      // [2 stages][2 halves] 128 softmax + 128 correction threads
   static constexpr int kBarAlpha = kBarPFull + 4;      // [2] basis published: 128 softmax threads
   static constexpr int kBarLReady = kBarAlpha + 2;     // [2] 128 softmax threads
   static constexpr int kBarODone = kBarLReady + 2;     // [2] tcgen05.commit
-  static constexpr int kNumBars = kBarODone + 2;
+  static constexpr int kBarLFree = kBarODone + 2;      // [2] 128 correction threads: the item's row sums are read
+  static constexpr int kNumBars = kBarLFree + 2;
   static constexpr int kOffTmemSlot = kOffBars + kNumBars * 8;
   static constexpr int kOffAbort = kOffTmemSlot + 8;
   static constexpr int kSmemBytes = kOffAbort + 8;   // the base must be 1024-byte aligned (checked)
@@ -279,62 +280,87 @@ __device__ __forceinline__ void fa_mma_role(const FaParams& p, uint32_t base, ui
                     T::v_lo(va, kk), T::kVHi, T::kIdescPV, (accumulate || kk != 0) ? 1u : 0u);
     }
   };
-  // First tile of an item: K_0 sits in slot KS; S_s = Q_s K_0^T for both stages.
-  auto first = [&](uint32_t KS, uint32_t qph, int nt_max) {
-    wait(bar(C::kBarQFull + 0), qph, kSiteMmaQFull);
-    wait(bar(C::kBarKvFull + KS), ring_ph, kSiteMmaKvFull);
-    tc_fence_after();
-    qk(0, KS);
-    wait(bar(C::kBarQFull + 1), qph, kSiteMmaQFull);
-    tc_fence_after();
-    qk(1, KS);
-    commit(bar(C::kBarKvFree + KS));
-    if (nt_max == 1) commit(bar(C::kBarQFree));
-  };
-  // Key tile j of an item: V_j sits in slot VS and, if there is a next tile, K_{j+1}
-  // in the slot behind it.
-  auto step = [&](uint32_t VS, int j, const int (&nt)[2]) {
-    const uint32_t KS = (VS + 1 == (uint32_t)kSlots) ? 0u : VS + 1;
-    const int nt_max = nt[1];
-    const bool has_next = (j + 1 < nt_max);
-    FA_TSTAMP(stamp_lane && blockIdx.x == 0 && item_i == 0, 2, j, 6);
-    wait(bar(C::kBarKvFull + VS), ring_ph, kSiteMmaKvFull);
-    if (has_next)
-      wait(bar(C::kBarKvFull + KS), KS == 0 ? (ring_ph ^ 1u) : ring_ph, kSiteMmaKvFull);
-    FA_TSTAMP(stamp_lane && blockIdx.x == 0 && item_i == 0, 2, j, 7);
-#pragma unroll
-    for (int s = 0; s < 2; ++s) {
-      if (!kCausal || j < nt[s]) {
-        FA_TSTAMP(stamp_lane && blockIdx.x == 0 && item_i == 0, 2, j, 3 * s + 0);
-        pv(s, VS, j > 0, cnt_pv[s] & 1u);
-        ++cnt_pv[s];
-        FA_TSTAMP(stamp_lane && blockIdx.x == 0 && item_i == 0, 2, j, 3 * s + 1);
-        if (j + 1 < nt[s]) qk(s, KS);
-        else commit(bar(C::kBarODone + s));
-        FA_TSTAMP(stamp_lane && blockIdx.x == 0 && item_i == 0, 2, j, 3 * s + 2);
-      }
-    }
-    commit(bar(C::kBarKvFree + VS));
-    if (has_next) commit(bar(C::kBarKvFree + KS));
-    if (j + 2 == nt_max) commit(bar(C::kBarQFree));   // last Q K^T issued
-  };
   auto advance = [&](uint32_t n) {
     slot += n;
     kv_count += n;
     if (slot >= (uint32_t)kSlots) { slot -= kSlots; ring_ph ^= 1u; }
   };
-  ItemIter<kCausal> items;
-  for (int mb, bh; items.next(p, mb, bh); ++item_i) {
-    int nt[2];
-    tile_counts<kCausal>(p, mb, nt[0], nt[1]);
-    const int nt_max = nt[1];
-    const uint32_t qph = item_i & 1u;
-    first(slot, qph, nt_max);
+  // First scores of an item for one stage: S_s = Q_s K_0^T with K_0 in slot KS (already
+  // waited for). `qph` is the phase of the item's Q loads, `nt_s` the stage's tile count.
+  auto first_qk = [&](int stage, uint32_t KS, uint32_t qph, int nt_s) {
+    wait(bar(C::kBarQFull + stage), qph, kSiteMmaQFull);
+    tc_fence_after();
+    qk(stage, KS);
+    if (nt_s == 1) commit(bar(C::kBarQFree + stage));   // also the stage's last Q K^T
+  };
+
+  // First tile of an item with the pipeline empty: K_0 sits in the current slot.
+  auto start_item = [&](uint32_t qph, const int (&nts)[2]) {
+    wait(bar(C::kBarKvFull + slot), ring_ph, kSiteMmaKvFull);
+    first_qk(0, slot, qph, nts[0]);
+    first_qk(1, slot, qph, nts[1]);
+    commit(bar(C::kBarKvFree + slot));
     advance(1);
+  };
+
+  // At head dim 128 the items form one stream: a stage's first Q K^T of the NEXT item is
+  // issued right behind its last P V of this one (for a causal item's shorter first
+  // stage, a whole tile earlier), so the stages keep alternating across the boundary
+  // instead of draining and refilling the pipeline once per item. A stage may therefore
+  // be a whole short item ahead of the correction warps; the per-item hand-overs that
+  // allow for it are the per-stage q_free and the l_free barrier. At head dim 64, where
+  // the MUFU rather than the issue order bounds a tile, this measured slower on causal
+  // problems, so there each item starts behind the previous one's last P V.
+  constexpr bool kStream = (D == 128);
+  ItemIter<kCausal> items;
+  int mb, bh, nt[2];
+  bool have = items.next(p, mb, bh);
+  if (have) {
+    tile_counts<kCausal>(p, mb, nt[0], nt[1]);
+    start_item(0u, nt);
+  }
+  while (have) {
+    int mb2, bh2, nt2[2] = {0, 0};
+    const bool have2 = items.next(p, mb2, bh2);
+    if (have2) tile_counts<kCausal>(p, mb2, nt2[0], nt2[1]);
+    const bool chain = kStream && have2;
+    const uint32_t qph2 = (item_i + 1u) & 1u;
+    const int nt_max = nt[1];
     for (int j = 0; j < nt_max; ++j) {
-      step(slot, j, nt);
-      advance(j + 1 < nt_max ? 2u : 1u);
+      // V_j sits in slot VS; behind it K_{j+1}, or a chained next item's K_0 after the last tile
+      const uint32_t VS = slot;
+      const uint32_t KS = (VS + 1 == (uint32_t)kSlots) ? 0u : VS + 1;
+      const bool last = (j + 1 == nt_max);
+      const bool need_k = !last || chain;
+      FA_TSTAMP(stamp_lane && blockIdx.x == 0 && item_i == 0, 2, j, 6);
+      wait(bar(C::kBarKvFull + VS), ring_ph, kSiteMmaKvFull);
+      if (need_k) wait(bar(C::kBarKvFull + KS), KS == 0 ? (ring_ph ^ 1u) : ring_ph, kSiteMmaKvFull);
+      FA_TSTAMP(stamp_lane && blockIdx.x == 0 && item_i == 0, 2, j, 7);
+#pragma unroll
+      for (int s = 0; s < 2; ++s) {
+        if (!kCausal || j < nt[s]) {
+          FA_TSTAMP(stamp_lane && blockIdx.x == 0 && item_i == 0, 2, j, 3 * s + 0);
+          pv(s, VS, j > 0, cnt_pv[s] & 1u);
+          ++cnt_pv[s];
+          FA_TSTAMP(stamp_lane && blockIdx.x == 0 && item_i == 0, 2, j, 3 * s + 1);
+          if (j + 1 < nt[s]) {
+            qk(s, KS);
+            if (j + 2 == nt[s]) commit(bar(C::kBarQFree + s));   // the stage's last Q K^T of this item
+          } else {
+            commit(bar(C::kBarODone + s));
+          }
+          FA_TSTAMP(stamp_lane && blockIdx.x == 0 && item_i == 0, 2, j, 3 * s + 2);
+        }
+        if (last && chain) first_qk(s, KS, qph2, nt2[s]);
+      }
+      commit(bar(C::kBarKvFree + VS));
+      if (need_k) commit(bar(C::kBarKvFree + KS));
+      advance(need_k ? 2u : 1u);
     }
+    have = have2;
+    mb = mb2; bh = bh2; nt[0] = nt2[0]; nt[1] = nt2[1];
+    ++item_i;
+    if (have && !kStream) start_item(item_i & 1u, nt);
   }
   if (p.dbg != nullptr && blockIdx.x == 0 && stamp_lane) {
     p.dbg[1] = kv_count;
@@ -382,7 +408,8 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
     *abort_flag = 0;
     mbar_init(bar(C::kBarQFull + 0), 1);
     mbar_init(bar(C::kBarQFull + 1), 1);
-    mbar_init(bar(C::kBarQFree), 1);
+    mbar_init(bar(C::kBarQFree + 0), 1);
+    mbar_init(bar(C::kBarQFree + 1), 1);
     for (int s = 0; s < C::kSlots; ++s) {
       mbar_init(bar(C::kBarKvFull + s), 1);
       mbar_init(bar(C::kBarKvFree + s), 1);
@@ -394,6 +421,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
       mbar_init(bar(C::kBarAlpha + s), 128);
       mbar_init(bar(C::kBarLReady + s), 128);
       mbar_init(bar(C::kBarODone + s), 1);
+      mbar_init(bar(C::kBarLFree + s), 128);
     }
     mbar_fence_init();
   }
@@ -434,11 +462,12 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
           const int kv_head = (bh - b_idx * p.heads_q) / (p.heads_q / p.heads_kv);
           const int kv_slice = b_idx * p.heads_kv + kv_head;
           const int q_row0 = mb * 2 * kAttnRows;   // within the head's sequence; rows past its end load as zeros
-          // Q may be overwritten once every S = Q K^T of the previous item has run
-          mbar_wait(bar(C::kBarQFree), (item_i & 1u) ^ 1u, wctx, kSiteLoadQFree);
+          // a stage's Q may be overwritten once its last S = Q K^T of the previous item has run
+          mbar_wait(bar(C::kBarQFree + 0), (item_i & 1u) ^ 1u, wctx, kSiteLoadQFree);
           mbar_arrive_expect_tx(bar(C::kBarQFull + 0), T::kTileBytes);
           T::load3(q_smem, &tmap_q, q_row0, bh, bar(C::kBarQFull + 0));
           kv_load(&tmap_k, 0, kv_slice);
+          mbar_wait(bar(C::kBarQFree + 1), (item_i & 1u) ^ 1u, wctx, kSiteLoadQFree);
           mbar_arrive_expect_tx(bar(C::kBarQFull + 1), T::kTileBytes);
           T::load3(q_smem + T::kTileBytes, &tmap_q, q_row0 + kAttnRows, bh, bar(C::kBarQFull + 1));
           for (int j = 0; j < nt1; ++j) {
@@ -467,7 +496,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
     const int row = tid & 127;
     const uint32_t t_row = tmem_addr(tmem, (warp & 3) * 32, C::kColS + stage * 128);
     const float scale_log2 = p.scale_log2;
-    uint32_t cnt_s = 0;
+    uint32_t cnt_s = 0, items_done = 0;
     ItemIter<kCausal> items;
     for (int mb, bh; items.next(p, mb, bh);) {
       int nt[2];
@@ -581,6 +610,10 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
         }
         l_run += (sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y);
       }
+      // the correction warps must have read the previous item's row sum (a stage may
+      // run a whole short item ahead of them)
+      if (items_done > 0) mbar_wait(bar(C::kBarLFree + stage), (items_done - 1u) & 1u, wctx, kSiteCorrLReady);
+      ++items_done;
       stats_l[stage * 128 + row] = l_run;
       mbar_arrive(bar(C::kBarLReady + stage));
     }
@@ -691,6 +724,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
         mbar_wait(bar(C::kBarLReady + s), item_i & 1u, wctx, kSiteCorrLReady);
         tc_fence_after();
         const float l_total = stats_l[s * 128 + row] + l_part[s];
+        mbar_arrive(bar(C::kBarLFree + s));   // the softmax warps may publish the next item's sum
         const float inv_l = 1.0f / l_total;
         if (p.lse != nullptr && row_valid) {
           // sum_j 2^(s_j c) = 2^(m c) * l with basis -m c in neg_prev: natural log of it
