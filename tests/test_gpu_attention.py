@@ -53,6 +53,17 @@ def test_many_items_per_cta(pkg, gpu, oracle_mod, D, causal):
     assert mx <= ATTN_MAX_ABS and mean <= ATTN_MEAN_ABS, (mx, mean)
 
 
+@pytest.mark.parametrize("S", [128, 256, 300])
+@pytest.mark.parametrize("D", [128, 64])
+@pytest.mark.parametrize("causal", [False, True])
+def test_many_short_items_per_cta(pkg, gpu, oracle_mod, S, D, causal):
+    """A dozen one- and two-tile items per CTA: the per-item hand-overs (Q buffers, row
+    sums, O accumulators) turn over as fast as they can, with a stage free to start the
+    next item while the other and the correction warps still finish this one."""
+    mx, mean = _run(pkg, gpu, oracle_mod, 8, 222, S, D, causal, sigma_qk=1.0)
+    assert mx <= ATTN_MAX_ABS and mean <= ATTN_MEAN_ABS, (mx, mean)
+
+
 @pytest.mark.parametrize("S", [128, 384, 640])
 @pytest.mark.parametrize("D,causal", [(128, False), (128, True), (64, True)])
 def test_odd_number_of_128_row_blocks(pkg, gpu, oracle_mod, S, D, causal):
