@@ -158,6 +158,7 @@ const char* ptxb200_strerror(int code) {
         "fa:mma.o_ready", "fa:softmax.s_full", "fa:corr.alpha", "fa:corr.l_ready",
         "fa:corr.o_done", "probe", "-", "shared memory base not 1024-byte aligned",
         "gemm2:empty", "gemm2:full", "gemm2:acc_empty", "gemm2:acc_full",
+        "fa:softmax.l_free",
     };
     unsigned site = ((unsigned)code >> 8) & 0xFFu;
     const char* name = site < sizeof(sites) / sizeof(sites[0]) ? sites[site] : "?";

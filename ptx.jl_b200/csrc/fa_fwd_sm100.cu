@@ -89,7 +89,7 @@ constexpr int kBatch = PTXB200_FA_BATCH;   // element pairs per exp batch
 enum : uint32_t {
   kSiteLoadQFree = 5, kSiteLoadKvFree = 6, kSiteMmaQFull = 7, kSiteMmaKvFull = 8,
   kSiteMmaPFull = 9, kSiteSoftmaxSFull = 11, kSiteCorrAlpha = 12,
-  kSiteCorrLReady = 13, kSiteCorrODone = 14
+  kSiteCorrLReady = 13, kSiteCorrODone = 14, kSiteSoftmaxLFree = 22
 };
 
 // Timestamp hooks for offline latency studies; compiled out of the product build.
@@ -612,7 +612,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
       }
       // the correction warps must have read the previous item's row sum (a stage may
       // run a whole short item ahead of them)
-      if (items_done > 0) mbar_wait(bar(C::kBarLFree + stage), (items_done - 1u) & 1u, wctx, kSiteCorrLReady);
+      if (items_done > 0) mbar_wait(bar(C::kBarLFree + stage), (items_done - 1u) & 1u, wctx, kSiteSoftmaxLFree);
       ++items_done;
       stats_l[stage * 128 + row] = l_run;
       mbar_arrive(bar(C::kBarLReady + stage));
