@@ -230,6 +230,48 @@ def test_grouped_heads_and_lse(pkg, gpu, oracle_mod, D, causal, H, H_kv):
     assert L.fa_fwd_bf16_ex(P, None, P, P, P, 1, 6, 4, 256, 128, ctypes.c_float(0.1), 0, 0, None, None) == pkg.native.E_SHAPE
 
 
+def _random_shapes(n, seed):
+    rng = np.random.default_rng(seed)
+    out = []
+    for i in range(n):
+        D = int(rng.choice([64, 128]))
+        causal = bool(rng.integers(0, 2))
+        S = int(rng.integers(1, 1400))
+        H_kv = int(rng.integers(1, 5))
+        H = H_kv * int(rng.integers(1, 4))
+        # enough (batch, head) slices that most CTAs walk several items of different length
+        B = max(1, int(rng.integers(150, 700)) // (H * max(1, (S + 255) // 256)))
+        out.append((B, H, H_kv, S, D, causal, 7000 + i))
+    return out
+
+
+@pytest.mark.parametrize("B,H,H_kv,S,D,causal,seed", _random_shapes(16, 20260025))
+def test_seeded_random_shapes(pkg, gpu, oracle_mod, B, H, H_kv, S, D, causal, seed):
+    """Shapes drawn from a seeded generator: any sequence length, grouped heads, both head
+    dims, causal or not, with the log-sum-exp output; O against the oracle, and the
+    default schedule bit for bit against single blocks for the causal ones."""
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(B, H, S, D, generator=g).to(torch.bfloat16)
+    k = torch.randn(B, H_kv, S, D, generator=g).to(torch.bfloat16)
+    v = torch.randn(B, H_kv, S, D, generator=g).to(torch.bfloat16)
+    qd, kd, vd = q.to(gpu), k.to(gpu), v.to(gpu)
+    lse = torch.full((B, H, S), float("nan"), dtype=torch.float32, device=gpu)
+    o = pkg.ops.fa_fwd(qd, kd, vd, causal=causal, lse=lse)
+    status = pkg.ops.sync_status()
+    assert status == 0, pkg.native.strerror(status)
+    assert not torch.isnan(lse).any()
+    ke = k.repeat_interleave(H // H_kv, dim=1)
+    ve = v.repeat_interleave(H // H_kv, dim=1)
+    ref = oracle_mod.attention_ref_c(bits(q).reshape(B * H, S, D), bits(ke).reshape(B * H, S, D),
+                                     bits(ve).reshape(B * H, S, D), 1.0 / D ** 0.5, causal)
+    mx, mean = attn_errors(o, ref)
+    assert mx <= ATTN_MAX_ABS and mean <= ATTN_MEAN_ABS, (mx, mean)
+    if causal:
+        o2 = pkg.ops.fa_fwd(qd, kd, vd, causal=True, flags=pkg.native.FA_SINGLE_BLOCKS)
+        assert pkg.ops.sync_status() == 0
+        assert torch.equal(o, o2)
+
+
 def test_rejects_bad_arguments(pkg, gpu):
     L = pkg.native.lib()
     t = torch.zeros(1, 1, 256, 128, dtype=torch.bfloat16, device=gpu)
