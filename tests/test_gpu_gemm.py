@@ -240,3 +240,35 @@ def test_grouped_gemm_pair_kernel(pkg, gpu):
     assert pkg.ops.sync_status() == 0
     assert torch.equal(c_pair, c_one)
     torch.testing.assert_close(c_pair, torch.bmm(a.float(), bt.float().transpose(1, 2)), rtol=1e-4, atol=1e-3)
+
+
+def _random_gemm_shapes(n, seed):
+    rng = np.random.default_rng(seed)
+    out = []
+    for _ in range(n):
+        M = 128 * int(rng.integers(1, 25))
+        N = 128 * int(rng.integers(1, 25))
+        K = 64 * int(rng.integers(1, 49))
+        out.append((M, N, K))
+    return out
+
+
+@pytest.mark.parametrize("M,N,K", _random_gemm_shapes(12, 20260026))
+def test_gemm_seeded_random_shapes(pkg, gpu, oracle_mod, M, N, K):
+    """Shapes drawn from a seeded generator, so that whichever schedule the dispatch picks
+    (one-CTA persistent, split along K, CTA pair) is checked against the oracle, and
+    against the one-CTA kernel without a split: bit for bit where the k-order per element
+    is the same (no split), to fp32 summation-order tolerance where it is not."""
+    g = torch.Generator().manual_seed(M * 7 + N * 3 + K)
+    a = (torch.randn(M, K, generator=g) * 0.1).to(torch.bfloat16)
+    bt = (torch.randn(N, K, generator=g) * 0.1).to(torch.bfloat16)
+    a_d, bt_d = a.to(gpu), bt.to(gpu)
+    c = pkg.ops.gemm(a_d, bt_d, f32_out=True)
+    c_plain = pkg.ops.gemm(a_d, bt_d, f32_out=True, no_split=True, one_cta=True)
+    c_nosplit = pkg.ops.gemm(a_d, bt_d, f32_out=True, no_split=True)
+    status = pkg.ops.sync_status()
+    assert status == 0, pkg.native.strerror(status)
+    assert torch.equal(c_nosplit, c_plain)
+    torch.testing.assert_close(c, c_plain, rtol=1e-4, atol=1e-4)
+    ref = oracle_mod.gemm_ref_c(bits(a), bits(bt))
+    np.testing.assert_allclose(c.cpu().numpy(), ref, rtol=1e-4, atol=1e-4)
