@@ -20,9 +20,10 @@
 //     stage's softmax warp does key columns 0-95 on the MUFU, the correction warp
 //     of the same rows does columns 96-127 with a polynomial on the FMA pipe;
 //   * a protocol of mbarrier phases in which no producer can run two phases ahead
-//     of its consumer: each producer's next arrival is downstream of an MMA issue
-//     that waited for the consumer's previous arrival, so no padding commits, no
-//     split-by-parity barriers and no "slot free" barriers are needed;
+//     of its consumer: within an item each producer's next arrival is downstream of
+//     an MMA issue that waited for the consumer's previous arrival, so no padding
+//     commits and no split-by-parity barriers are needed; across items, where a
+//     stage may run a short item ahead, the row sums are handed over through l_free;
 //   * every wait is bounded and reports to a status word.
 //
 // Roles (512 threads): warps 0-3 / 4-7 softmax of stage 0 / 1 (thread = one row),
