@@ -79,8 +79,11 @@ const char* ptxb200_last_cuda_error(void);
  * Few tiles, long K: when the 128x256 output tiles number at most half the SMs and
  * K is long enough, every tile is cut along K and shared by at least twice as many
  * SMs; the partial sums meet in fp32 scratch that the library keeps per (device,
- * stream), allocated by the first launch that needs it (about 38 MB) and freed by
- * ptxb200_shutdown, and a second small kernel on the same stream adds them up.
+ * stream) -- 256 KiB per CTA of the launch, at most 38 MB, allocated (cudaMalloc) by
+ * the first launch on a stream that needs it, so make that launch outside stream
+ * capture or pass PTXB200_GEMM_NO_SPLIT; at most 16 such buffers exist per process (the
+ * least recently used one is waited for and freed when a 17th stream asks), all freed
+ * by ptxb200_shutdown -- and a second small kernel on the same stream adds them up.
  * Results stay reproducible from launch to launch; they differ in the last bits from
  * the unsplit summation order, which PTXB200_GEMM_NO_SPLIT keeps. No reference
  * counterpart (test/gpu/blackwell/gemm_highperf_blackwell.jl:27-32 leaves it).
@@ -216,20 +219,48 @@ int fa_fwd_bf16_ex(void* O, void* lse, const void* Q, const void* K, const void*
  *     the status word and flags. The attention results themselves do not depend
  *     on the scratch contents unless a wait runs out.
  *   - ptxb200_sync_status() reports on fa_fwd_bf16/gemm_bf16 launches only; it
- *     does not read this array (it would allocate the workspace).
+ *     does not read this array (it would allocate the workspace). Use
+ *     fa_fwd_bf16_noalloc_status() below.
  */
 int fa_fwd_bf16_noalloc(void* O, const void* Q, const void* K, const void* V, int B, int H, int S,
                         int D, float sm_scale, int causal, unsigned flags, void* stream);
 
 /*
- * Synchronise `stream`, then return and clear the current device's status word:
- * 0 if every kernel enqueued through this library since the last call ran to
- * completion normally, a positive code if a bounded device-side wait ran out
- * (the affected outputs are then invalid), PTXB200_E_CUDA if the stream itself
- * reports an error. Replaces the reference's beacon buffer read-back
- * (flash_attention_defs.jl:224-267, 989-998).
+ * The status read-back that goes with fa_fwd_bf16_noalloc, and like it allocates
+ * nothing (no counterpart in the reference; its beacon read-back,
+ * flash_attention_defs.jl:989-998, copies a buffer the caller allocated).
+ *
+ * Waits for `stream`, then copies the static array of the current device to the host:
+ * returns its status word -- 0 if every bounded wait of the fa_fwd_bf16_noalloc
+ * launches since the last read completed, else the positive first-blame code
+ * (ptxb200_strerror decodes it; the outputs of that launch are invalid) -- and clears
+ * the word when it was nonzero. If cta_flags_out is not NULL it receives
+ * min(max_flags, 240) words, word i nonzero iff a wait ran out in CTA i of the most
+ * recent launch (each launch clears the flags it uses). Before any
+ * fa_fwd_bf16_noalloc call on the device it returns 0. The sharing rule of the
+ * array applies: a read that overlaps a launch on another stream races with it.
+ */
+int fa_fwd_bf16_noalloc_status(uint32_t* cta_flags_out, int max_flags, void* stream);
+
+/*
+ * Synchronise `stream`, then return and clear that stream's status word on the
+ * current device: 0 if every kernel enqueued on `stream` through this library since
+ * the last call ran to completion normally, a positive code if a bounded device-side
+ * wait ran out (the affected outputs are then invalid), PTXB200_E_CUDA if the stream
+ * itself reports an error. Each stream that launches through the library gets a word of
+ * its own (the first 128 streams per device; beyond that, streams share words by hash
+ * and a read may then report a neighbour's failure). Replaces the reference's beacon
+ * buffer read-back (flash_attention_defs.jl:224-267, 989-998).
  */
 int ptxb200_sync_status(void* stream);
+
+/*
+ * The same for every stream at once: synchronises the current DEVICE, returns the
+ * first nonzero status word of any stream that launched through this library on it
+ * (0 if none) and clears them all. For callers that launch on several streams and check
+ * once at the end. No reference counterpart beyond the one above.
+ */
+int ptxb200_device_status(void);
 
 /*
  * Bring-up probes with known answers, restating the reference's single-

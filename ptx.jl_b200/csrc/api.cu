@@ -3,6 +3,7 @@
 #include <cstdio>
 #include <cstring>
 #include <mutex>
+#include <unordered_map>
 #include <vector>
 
 #include "host_common.h"
@@ -26,12 +27,17 @@ const char* get_cuda_error() { return g_err; }
 // ---------------------------------------------------------------------------
 static std::mutex g_mu;
 static std::vector<DeviceCtx*> g_ctx;  // indexed by device ordinal
+// status slot of every stream seen per device (guarded by g_mu)
+static std::vector<std::unordered_map<cudaStream_t, int>> g_slots;
 
 int current_ctx(DeviceCtx** out) {
   int dev = -1;
   PTXB200_CUDA_TRY(cudaGetDevice(&dev));
   std::lock_guard<std::mutex> lock(g_mu);
-  if ((int)g_ctx.size() <= dev) g_ctx.resize(dev + 1, nullptr);
+  if ((int)g_ctx.size() <= dev) {
+    g_ctx.resize(dev + 1, nullptr);
+    g_slots.resize(dev + 1);
+  }
   if (g_ctx[dev] == nullptr) {
     DeviceCtx c;
     c.device = dev;
@@ -50,8 +56,23 @@ int current_ctx(DeviceCtx** out) {
   return PTXB200_OK;
 }
 
+uint32_t* status_word(const DeviceCtx& ctx, cudaStream_t stream) {
+  std::lock_guard<std::mutex> lock(g_mu);
+  auto& slots = g_slots[ctx.device];
+  auto it = slots.find(stream);
+  if (it == slots.end()) {
+    const int next = (int)slots.size();
+    // every slot taken: share by hash (a status read may then name a neighbour's failure)
+    const int slot = next < kWsStatusSlots
+                         ? next
+                         : (int)((reinterpret_cast<uintptr_t>(stream) * 0x9E3779B97F4A7C15ull) >> 57) % kWsStatusSlots;
+    it = slots.emplace(stream, slot).first;
+  }
+  return ctx.workspace + it->second;
+}
+
 int release_all_ctx() {
-  gemm_release_scratch();
+  scratch_release_all();
   std::lock_guard<std::mutex> lock(g_mu);
   int prev = -1;
   cudaGetDevice(&prev);
@@ -61,8 +82,102 @@ int release_all_ctx() {
     delete c;
     c = nullptr;
   }
+  for (auto& m : g_slots) m.clear();
   if (prev >= 0) cudaSetDevice(prev);
   return PTXB200_OK;
+}
+
+// ---------------------------------------------------------------------------
+// scratch buffers per (device, stream, purpose)
+// ---------------------------------------------------------------------------
+namespace {
+struct ScratchEntry {
+  bool live = false;
+  int device = -1;
+  cudaStream_t stream = nullptr;
+  int kind = 0;
+  void* ptr = nullptr;
+  size_t bytes = 0;
+  cudaEvent_t done = nullptr;   // recorded behind the last launch that used the buffer
+  bool recorded = false;
+  unsigned long long last_use = 0;
+};
+std::mutex g_scratch_mu;
+ScratchEntry g_scratch[kScratchMaxEntries];
+unsigned long long g_scratch_clock = 0;
+
+// Waits for the entry's last user and frees its buffer (its device must be current or
+// is made current for the call). Lock held by the caller.
+void scratch_drop(ScratchEntry& e) {
+  if (!e.live) return;
+  int prev = -1;
+  cudaGetDevice(&prev);
+  if (prev != e.device) cudaSetDevice(e.device);
+  if (e.recorded) cudaEventSynchronize(e.done);
+  if (e.ptr != nullptr) cudaFree(e.ptr);
+  if (e.done != nullptr) cudaEventDestroy(e.done);
+  if (prev >= 0 && prev != e.device) cudaSetDevice(prev);
+  e = ScratchEntry();
+}
+}  // namespace
+
+int scratch_acquire(const DeviceCtx& ctx, cudaStream_t stream, int kind, size_t bytes, ScratchLease* out) {
+  std::lock_guard<std::mutex> lock(g_scratch_mu);
+  int hit = -1, free_slot = -1, lru = -1;
+  for (int i = 0; i < kScratchMaxEntries; ++i) {
+    ScratchEntry& e = g_scratch[i];
+    if (!e.live) {
+      if (free_slot < 0) free_slot = i;
+      continue;
+    }
+    if (e.device == ctx.device && e.stream == stream && e.kind == kind) hit = i;
+    if (lru < 0 || e.last_use < g_scratch[lru].last_use) lru = i;
+  }
+  if (hit >= 0 && g_scratch[hit].bytes < bytes) {
+    scratch_drop(g_scratch[hit]);   // too small: wait for its last user, then allocate anew
+    free_slot = hit;
+    hit = -1;
+  }
+  if (hit < 0) {
+    if (free_slot < 0) {
+      scratch_drop(g_scratch[lru]);
+      free_slot = lru;
+    }
+    ScratchEntry& e = g_scratch[free_slot];
+    PTXB200_CUDA_TRY(cudaMalloc(&e.ptr, bytes));
+    cudaError_t ee = cudaEventCreateWithFlags(&e.done, cudaEventDisableTiming);
+    if (ee != cudaSuccess) {
+      cudaFree(e.ptr);
+      e = ScratchEntry();
+      set_cuda_error("cudaEventCreateWithFlags", ee);
+      return PTXB200_E_CUDA;
+    }
+    e.live = true;
+    e.device = ctx.device;
+    e.stream = stream;
+    e.kind = kind;
+    e.bytes = bytes;
+    hit = free_slot;
+  }
+  g_scratch[hit].last_use = ++g_scratch_clock;
+  out->ptr = g_scratch[hit].ptr;
+  out->entry = hit;
+  return PTXB200_OK;
+}
+
+int scratch_mark_used(const ScratchLease& lease, cudaStream_t stream) {
+  std::lock_guard<std::mutex> lock(g_scratch_mu);
+  if (lease.entry < 0 || lease.entry >= kScratchMaxEntries) return PTXB200_E_INVALID;
+  ScratchEntry& e = g_scratch[lease.entry];
+  if (!e.live || e.ptr != lease.ptr) return PTXB200_OK;   // recycled meanwhile by another thread's eviction
+  PTXB200_CUDA_TRY(cudaEventRecord(e.done, stream));
+  e.recorded = true;
+  return PTXB200_OK;
+}
+
+void scratch_release_all() {
+  std::lock_guard<std::mutex> lock(g_scratch_mu);
+  for (ScratchEntry& e : g_scratch) scratch_drop(e);
 }
 
 // ---------------------------------------------------------------------------
@@ -262,7 +377,7 @@ int fa_fwd_bf16_ex(void* O, void* lse, const void* Q, const void* K, const void*
   int rc = current_ctx(&ctx);
   if (rc != PTXB200_OK) return rc;
   return launch_fa_fwd(*ctx, O, lse, Q, K, V, B, H, H_kv, S, D, sm_scale, causal, flags, dbg,
-                       ctx->workspace + kWsStatus, (cudaStream_t)stream);
+                       status_word(*ctx, (cudaStream_t)stream), (cudaStream_t)stream);
 }
 
 int fa_fwd_bf16(void* O, const void* Q, const void* K, const void* V, int B, int H, int S, int D,
@@ -275,15 +390,28 @@ int ptxb200_sync_status(void* stream) {
   int rc = current_ctx(&ctx);
   if (rc != PTXB200_OK) return rc;
   cudaStream_t s = (cudaStream_t)stream;
+  uint32_t* slot = status_word(*ctx, s);
   uint32_t word = 0;
-  PTXB200_CUDA_TRY(cudaMemcpyAsync(&word, ctx->workspace + kWsStatus, sizeof(word),
-                                   cudaMemcpyDeviceToHost, s));
+  PTXB200_CUDA_TRY(cudaMemcpyAsync(&word, slot, sizeof(word), cudaMemcpyDeviceToHost, s));
   PTXB200_CUDA_TRY(cudaStreamSynchronize(s));
   if (word != 0) {
-    PTXB200_CUDA_TRY(cudaMemsetAsync(ctx->workspace + kWsStatus, 0, sizeof(word), s));
+    PTXB200_CUDA_TRY(cudaMemsetAsync(slot, 0, sizeof(word), s));
     PTXB200_CUDA_TRY(cudaStreamSynchronize(s));
   }
   return (int)word;
+}
+
+int ptxb200_device_status(void) {
+  DeviceCtx* ctx = nullptr;
+  int rc = current_ctx(&ctx);
+  if (rc != PTXB200_OK) return rc;
+  PTXB200_CUDA_TRY(cudaDeviceSynchronize());
+  uint32_t words[kWsStatusSlots];
+  PTXB200_CUDA_TRY(cudaMemcpy(words, ctx->workspace, sizeof(words), cudaMemcpyDeviceToHost));
+  uint32_t first = 0;
+  for (int i = 0; i < kWsStatusSlots && first == 0; ++i) first = words[i];
+  if (first != 0) PTXB200_CUDA_TRY(cudaMemset(ctx->workspace, 0, sizeof(words)));
+  return (int)first;
 }
 
 int ptxb200_selftest(int which, void* out_s, void* out_o, const void* q, const void* k,

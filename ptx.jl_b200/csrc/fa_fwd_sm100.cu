@@ -806,8 +806,8 @@ template <int D, bool kCausal>
 int launch_variant(const DeviceCtx& ctx, const CUtensorMap& tq, const CUtensorMap& tk,
                    const CUtensorMap& tv, const FaParams& p, cudaStream_t stream) {
   using C = FaCfg<D>;
-  static bool attr_done[64] = {false};
-  if (!attr_done[ctx.device & 63]) {
+  static PerDeviceOnce attr_once;   // one per <D, kCausal> instantiation
+  const int rc = attr_once.run(ctx.device, []() -> int {
     PTXB200_CUDA_TRY(cudaFuncSetAttribute(fa_fwd_kernel<D, kCausal>,
                                           cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           C::kSmemBytes));
@@ -815,8 +815,9 @@ int launch_variant(const DeviceCtx& ctx, const CUtensorMap& tq, const CUtensorMa
       PTXB200_CUDA_TRY(cudaFuncSetAttribute(fa_fwd_kernel<D, false, false, true>,
                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
                                             C::kSmemBytes));
-    attr_done[ctx.device & 63] = true;
-  }
+    return PTXB200_OK;
+  });
+  if (rc != PTXB200_OK) return rc;
   const int units = (kCausal && p.pair_mode) ? p.bh * ((p.num_mblocks + 1) / 2) : p.total_work;   // what ItemIter deals out
   const int grid = units < ctx.sm_count ? units : ctx.sm_count;
   if (!kCausal && p.seqlen % kAttnRows != 0)
@@ -1015,3 +1016,40 @@ extern "C" int fa_fwd_bf16_noalloc(void* O, const void* Q, const void* K, const 
                 : noalloc_launch<64, false>(tq, tk, tv, p, grid, stream);
 }
 
+
+// Reads back what fa_fwd_bf16_noalloc launches on the current device left in the static
+// array, without allocating: waits for `stream`, copies the status word and the per-CTA
+// flags to the caller's host memory and returns the word (0 = every wait completed).
+extern "C" int fa_fwd_bf16_noalloc_status(uint32_t* cta_flags_out, int max_flags, void* stream_v) {
+  using namespace ptxb200;
+  if (max_flags < 0 || (cta_flags_out == nullptr && max_flags > 0)) return PTXB200_E_INVALID;
+  cudaStream_t stream = (cudaStream_t)stream_v;
+  int dev = -1;
+  PTXB200_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kNoAllocMaxDevices) {
+    set_error_text("fa_fwd_bf16_noalloc_status: device ordinal beyond the 64 this entry point tracks");
+    return PTXB200_E_CAPACITY;
+  }
+  uint32_t* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_noalloc_mu);
+    if (g_noalloc_dev[dev].ready) scratch = g_noalloc_dev[dev].scratch;
+  }
+  const int n_flags = max_flags < kNoAllocMaxCtas ? max_flags : kNoAllocMaxCtas;
+  if (scratch == nullptr) {
+    // no fa_fwd_bf16_noalloc launch on this device yet: nothing to report
+    PTXB200_CUDA_TRY(cudaStreamSynchronize(stream));
+    for (int i = 0; i < n_flags; ++i) cta_flags_out[i] = 0;
+    return PTXB200_OK;
+  }
+  uint32_t host[kNoAllocScratchWords];
+  PTXB200_CUDA_TRY(cudaMemcpyAsync(host, scratch, sizeof(host), cudaMemcpyDeviceToHost, stream));
+  PTXB200_CUDA_TRY(cudaStreamSynchronize(stream));
+  for (int i = 0; i < n_flags; ++i) cta_flags_out[i] = host[kNoAllocFlagBase + i];
+  if (host[0] != 0) {
+    // first blame is consumed by this read, as with ptxb200_sync_status
+    PTXB200_CUDA_TRY(cudaMemsetAsync(scratch, 0, sizeof(uint32_t), stream));
+    PTXB200_CUDA_TRY(cudaStreamSynchronize(stream));
+  }
+  return (int)host[0];
+}

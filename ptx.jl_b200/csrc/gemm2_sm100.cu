@@ -303,18 +303,17 @@ int launch_gemm_pair(const DeviceCtx& ctx, void* C, const void* A, const void* B
   const long long tiles = (long long)groups * ((M + kBM2 - 1) / kBM2) * ((N + kBN2 - 1) / kBN2);
   const int max_pairs = ctx.sm_count / 2;
   const int pairs = tiles < max_pairs ? (int)tiles : max_pairs;
-  uint32_t* status = ctx.workspace + kWsStatus;
-  static bool attr_done[2][64] = {{false}};
+  uint32_t* status = status_word(ctx, stream);
   const int f32 = (flags & PTXB200_GEMM_F32_OUT) ? 1 : 0;
-  if (!attr_done[f32][ctx.device & 63]) {
-    if (f32)
-      PTXB200_CUDA_TRY(cudaFuncSetAttribute(gemm_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                            kSmemBytes2));
-    else
-      PTXB200_CUDA_TRY(cudaFuncSetAttribute(gemm_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                            kSmemBytes2));
-    attr_done[f32][ctx.device & 63] = true;
-  }
+  static PerDeviceOnce attr_once;
+  rc = attr_once.run(ctx.device, []() -> int {
+    PTXB200_CUDA_TRY(cudaFuncSetAttribute(gemm_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          kSmemBytes2));
+    PTXB200_CUDA_TRY(cudaFuncSetAttribute(gemm_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          kSmemBytes2));
+    return PTXB200_OK;
+  });
+  if (rc != PTXB200_OK) return rc;
   if (f32)
     gemm_pair_kernel<true><<<2 * pairs, kThreads2, kSmemBytes2, stream>>>(ta, tb, C, M, N, K, ldc, groups, status);
   else

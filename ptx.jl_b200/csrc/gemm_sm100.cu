@@ -355,35 +355,13 @@ sk_reduce_kernel(void* __restrict__ c_out, int M, int N, int ldc, int tiles_m, i
 
 namespace {
 
-// fp32 slabs for tiles cut along K, one set per (device, stream): launches on one
-// stream run one after the other, launches on different streams may overlap and must
-// not share them. Allocated on the first launch that needs them, freed by
-// ptxb200_shutdown.
-std::mutex g_sk_mu;
-std::map<std::pair<int, cudaStream_t>, float*> g_sk;
-
-int sk_scratch(const DeviceCtx& ctx, cudaStream_t stream, float** out) {
-  std::lock_guard<std::mutex> lock(g_sk_mu);
-  float*& slabs = g_sk[{ctx.device, stream}];
-  if (slabs == nullptr)
-    PTXB200_CUDA_TRY(cudaMalloc((void**)&slabs, (size_t)2 * ctx.sm_count * kBM * kBN * sizeof(float)));
-  *out = slabs;
-  return PTXB200_OK;
-}
-
+// The fp32 slabs for tiles cut along K come from the library's per-(device, stream)
+// scratch (scratch_acquire): launches on one stream run one after the other, launches
+// on different streams may overlap and must not share them. A launch needs two slabs
+// per CTA.
 constexpr int kSkMinIters = 8;   // a CTA's share of the k-iteration line is at least this long
 
 }  // namespace
-
-void gemm_release_scratch() {
-  std::lock_guard<std::mutex> lock(g_sk_mu);
-  int prev = -1;
-  cudaGetDevice(&prev);
-  for (auto& kv : g_sk)
-    if (kv.second != nullptr && cudaSetDevice(kv.first.first) == cudaSuccess) cudaFree(kv.second);
-  g_sk.clear();
-  if (prev >= 0) cudaSetDevice(prev);
-}
 
 int launch_gemm(const DeviceCtx& ctx, void* C, const void* A, const void* Bt, int groups, int M, int N,
                 int K, int ldc, unsigned flags, cudaStream_t stream) {
@@ -405,6 +383,7 @@ int launch_gemm(const DeviceCtx& ctx, void* C, const void* A, const void* Bt, in
   sched.sk_ctas = 0;
   sched.slabs = nullptr;
   int grid = tiles < ctx.sm_count ? tiles : ctx.sm_count;
+  ScratchLease lease;
   // Few tiles, long K: cut every tile along K so that at least twice as many CTAs work.
   // (Cutting only the tiles of a sparse LAST wave was built too and measured slower
   // than leaving them whole: parking and re-reading two partial tiles per CTA costs
@@ -414,31 +393,28 @@ int launch_gemm(const DeviceCtx& ctx, void* C, const void* A, const void* Bt, in
     long long ctas = line / kSkMinIters;
     if (ctas > ctx.sm_count) ctas = ctx.sm_count;
     if (ctas >= 2 * tiles) {
-      if ((rc = sk_scratch(ctx, stream, &sched.slabs)) != PTXB200_OK) return rc;
+      if ((rc = scratch_acquire(ctx, stream, kScratchGemmSlabs, (size_t)2 * ctas * kBM * kBN * sizeof(float),
+                                &lease)) != PTXB200_OK)
+        return rc;
+      sched.slabs = reinterpret_cast<float*>(lease.ptr);
       sched.dp_tiles = 0;
       sched.sk_tiles = tiles;
       sched.sk_ctas = (int)ctas;
       grid = (int)ctas;
     }
   }
-  uint32_t* status = ctx.workspace + kWsStatus;
-  if (flags & PTXB200_GEMM_F32_OUT) {
-    static bool attr_done_f32[64] = {false};
-    if (!attr_done_f32[ctx.device & 63]) {
-      PTXB200_CUDA_TRY(cudaFuncSetAttribute(gemm_kernel<true>,
-                                            cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-      attr_done_f32[ctx.device & 63] = true;
-    }
+  uint32_t* status = status_word(ctx, stream);
+  static PerDeviceOnce attr_once;
+  rc = attr_once.run(ctx.device, []() -> int {
+    PTXB200_CUDA_TRY(cudaFuncSetAttribute(gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    PTXB200_CUDA_TRY(cudaFuncSetAttribute(gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    return PTXB200_OK;
+  });
+  if (rc != PTXB200_OK) return rc;
+  if (flags & PTXB200_GEMM_F32_OUT)
     gemm_kernel<true><<<grid, kThreads, kSmemBytes, stream>>>(ta, tb, C, M, N, K, ldc, groups, sched, status);
-  } else {
-    static bool attr_done_bf16[64] = {false};
-    if (!attr_done_bf16[ctx.device & 63]) {
-      PTXB200_CUDA_TRY(cudaFuncSetAttribute(gemm_kernel<false>,
-                                            cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-      attr_done_bf16[ctx.device & 63] = true;
-    }
+  else
     gemm_kernel<false><<<grid, kThreads, kSmemBytes, stream>>>(ta, tb, C, M, N, K, ldc, groups, sched, status);
-  }
   PTXB200_CUDA_TRY(cudaGetLastError());
   if (sched.sk_tiles > 0) {
     const long long items = (long long)sched.sk_tiles * (kBN / 4) * kBM;
@@ -448,6 +424,7 @@ int launch_gemm(const DeviceCtx& ctx, void* C, const void* A, const void* Bt, in
     else
       sk_reduce_kernel<false><<<rgrid, 256, 0, stream>>>(C, M, N, ldc, tiles_m, tiles_n, sched);
     PTXB200_CUDA_TRY(cudaGetLastError());
+    if ((rc = scratch_mark_used(lease, stream)) != PTXB200_OK) return rc;
   }
   return PTXB200_OK;
 }

@@ -11,14 +11,20 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <mutex>
+#include <vector>
+
 #include "../../include/ptxb200.h"
 
 namespace ptxb200 {
 
-// Words of the per-device workspace (uint32 each).
+// Words of the per-device workspace (uint32 each): one first-blame status word per
+// stream that has launched through the library on the device (slot 0 .. kWsStatusSlots-1,
+// handed out in order of first use; once every slot is taken further streams share
+// slots by hash).
 enum : int {
-  kWsStatus = 0,       // first-blame status word written by bounded waits
-  kWsWords = 64,
+  kWsStatusSlots = 128,
+  kWsWords = 256,
 };
 
 struct DeviceCtx {
@@ -28,6 +34,53 @@ struct DeviceCtx {
   int cc_minor = 0;
   uint32_t* workspace = nullptr;  // kWsWords uint32 on the device, zero-initialised once
 };
+
+// Device address of the status word that launches on `stream` report to.
+uint32_t* status_word(const DeviceCtx& ctx, cudaStream_t stream);
+
+// Runs `f` (returning PTXB200_OK or an error code) once per device ordinal, under a lock;
+// later calls for that device return PTXB200_OK at once. For the per-kernel
+// cudaFuncSetAttribute calls of the launchers.
+class PerDeviceOnce {
+ public:
+  template <class F>
+  int run(int device, F&& f) {
+    if (device < 0) return PTXB200_E_INVALID;
+    std::lock_guard<std::mutex> lock(mu_);
+    if ((int)done_.size() <= device) done_.resize(device + 1, 0);
+    if (!done_[device]) {
+      const int rc = f();
+      if (rc != PTXB200_OK) return rc;
+      done_[device] = 1;
+    }
+    return PTXB200_OK;
+  }
+
+ private:
+  std::mutex mu_;
+  std::vector<char> done_;
+};
+
+// Scratch memory the library keeps per (device, stream, purpose) for kernels that park
+// partial results in global memory: launches on one stream run one after the other and
+// may share a buffer, launches on different streams may overlap and must not.
+//  * scratch_acquire returns a buffer of at least `bytes` for (current device, stream,
+//    kind), allocating or growing it when needed (cudaMalloc: the first such launch on a
+//    stream must come outside stream capture).
+//  * scratch_mark_used, called after the kernels that use the buffer are enqueued, records
+//    an event so that the buffer can later be recycled safely.
+//  * At most kScratchMaxEntries buffers exist per process: when a new (device, stream,
+//    kind) needs one and the table is full, the least recently used entry is waited for
+//    (its event) and freed. Everything is freed by ptxb200_shutdown.
+enum : int { kScratchGemmSlabs = 0, kScratchAttnParts = 1 };
+constexpr int kScratchMaxEntries = 16;
+struct ScratchLease {
+  void* ptr = nullptr;
+  int entry = -1;
+};
+int scratch_acquire(const DeviceCtx& ctx, cudaStream_t stream, int kind, size_t bytes, ScratchLease* out);
+int scratch_mark_used(const ScratchLease& lease, cudaStream_t stream);
+void scratch_release_all();
 
 // Context of the device current in the calling thread (created on first use).
 // Returns PTXB200_OK or a negative code.
@@ -72,8 +125,6 @@ int launch_fa_fwd(const DeviceCtx& ctx, void* O, void* lse, const void* Q, const
 bool gemm_pair_eligible(const DeviceCtx& ctx, int groups, int M, int N, int K);
 int launch_gemm_pair(const DeviceCtx& ctx, void* C, const void* A, const void* Bt, int groups, int M, int N,
                      int K, int ldc, unsigned flags, cudaStream_t stream);
-// Frees the stream-K scratch of every (device, stream) that used it.
-void gemm_release_scratch();
 // Row-wise fp32 kernels; op: 0 softmax, 1 RMS norm, 2 layer norm.
 int launch_rowwise(const DeviceCtx& ctx, int op, float* y, const float* x, const float* w,
                    const float* bias, int rows, int n, float eps, cudaStream_t stream);

@@ -162,7 +162,7 @@ int launch_tile_probe(const DeviceCtx& ctx, void* out_s, void* out_o, const void
                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
   attn_tile_probe_kernel<D><<<1, 128, smem_bytes, stream>>>(
       tq, tk, tv, reinterpret_cast<const uint32_t*>(p), reinterpret_cast<float*>(out_s),
-      reinterpret_cast<float*>(out_o), ctx.workspace + kWsStatus);
+      reinterpret_cast<float*>(out_o), status_word(ctx, stream));
   PTXB200_CUDA_TRY(cudaGetLastError());
   return PTXB200_OK;
 }
@@ -204,7 +204,7 @@ int launch_selftest(const DeviceCtx& ctx, int which, void* out_s, void* out_o, c
     case 1: return launch_tile_probe<128>(ctx, out_s, out_o, q, k, v, p, stream);
     case 2: return launch_tile_probe<64>(ctx, out_s, out_o, q, k, v, p, stream);
     case 3:
-      wait_expiry_kernel<<<1, 32, 0, stream>>>(reinterpret_cast<uint32_t*>(out_s), ctx.workspace + kWsStatus);
+      wait_expiry_kernel<<<1, 32, 0, stream>>>(reinterpret_cast<uint32_t*>(out_s), status_word(ctx, stream));
       PTXB200_CUDA_TRY(cudaGetLastError());
       return PTXB200_OK;
     default: return PTXB200_E_INVALID;

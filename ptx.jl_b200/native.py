@@ -78,8 +78,12 @@ def lib() -> ctypes.CDLL:
     L.fa_fwd_bf16_ex.argtypes = [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, cf, ci, cu, vp, vp]
     L.fa_fwd_bf16_noalloc.restype = ci
     L.fa_fwd_bf16_noalloc.argtypes = [vp, vp, vp, vp, ci, ci, ci, ci, cf, ci, cu, vp]
+    L.fa_fwd_bf16_noalloc_status.restype = ci
+    L.fa_fwd_bf16_noalloc_status.argtypes = [vp, ci, vp]
     L.ptxb200_sync_status.restype = ci
     L.ptxb200_sync_status.argtypes = [vp]
+    L.ptxb200_device_status.restype = ci
+    L.ptxb200_device_status.argtypes = []
     L.ptxb200_selftest.restype = ci
     L.ptxb200_selftest.argtypes = [ci, vp, vp, vp, vp, vp, vp, vp]
     L.ptxb200_shutdown.restype = ci
@@ -101,5 +105,11 @@ def check(code: int) -> None:
 
 
 def sync_status(stream: int = 0) -> int:
-    """Synchronise the stream and return (and clear) the device status word."""
+    """Synchronise the stream and return (and clear) its status word."""
     return lib().ptxb200_sync_status(ctypes.c_void_p(stream))
+
+
+def device_status() -> int:
+    """Synchronise the current device and return (and clear) the first nonzero status
+    word of any stream that launched through the library on it."""
+    return lib().ptxb200_device_status()

@@ -20,17 +20,38 @@ def _ptr(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
     return ctypes.c_void_p(0 if t is None else t.data_ptr())
 
 
-def _stream(stream: Optional[torch.cuda.Stream]) -> ctypes.c_void_p:
-    s = torch.cuda.current_stream() if stream is None else stream
+def _stream(stream: Optional[torch.cuda.Stream], device=None) -> ctypes.c_void_p:
+    s = torch.cuda.current_stream(device) if stream is None else stream
     return ctypes.c_void_p(s.cuda_stream)
 
 
-def _require_cuda(*tensors: torch.Tensor) -> None:
+def _require_cuda(*tensors) -> None:
+    """Every tensor is a contiguous CUDA tensor and all of them live on one device."""
     for t in tensors:
         if not t.is_cuda:
             raise ValueError("ptxb200 ops take CUDA tensors (the library has no CPU path)")
         if not t.is_contiguous():
             raise ValueError("ptxb200 ops take contiguous tensors")
+    if len({t.device for t in tensors}) > 1:
+        raise ValueError("ptxb200 ops take tensors of ONE device; got " +
+                         ", ".join(sorted({str(t.device) for t in tensors})))
+
+
+def _check_out(out, like_device, shape, dtype, what: str = "out") -> None:
+    """A caller-supplied output buffer the kernel will write `shape` elements of `dtype`
+    into: anything else would be an out-of-bounds or mistyped device write."""
+    _require_cuda(out)
+    if out.device != like_device:
+        raise ValueError(f"{what} must live on {like_device}, not {out.device}")
+    if tuple(out.shape) != tuple(shape):
+        raise ValueError(f"{what} must have shape {tuple(shape)}, not {tuple(out.shape)}")
+    if out.dtype != dtype:
+        raise ValueError(f"{what} must be {dtype}, not {out.dtype}")
+
+
+def _check_stream(stream, device) -> None:
+    if stream is not None and getattr(stream, "device", device) != device:
+        raise ValueError(f"stream belongs to {stream.device}, the tensors to {device}")
 
 
 def fa_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: bool = False,
@@ -54,19 +75,25 @@ def fa_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: bool = 
     H_kv = k.shape[1]
     if lse is not None:
         _require_cuda(lse)
-        if lse.dtype != torch.float32 or lse.numel() != B * H * S:
-            raise ValueError("lse must be B*H*S float32")
+        if lse.device != q.device or lse.dtype != torch.float32 or lse.numel() != B * H * S:
+            raise ValueError("lse must be B*H*S float32 on the tensors' device")
+    if dbg is not None:
+        _require_cuda(dbg)
+        if dbg.device != q.device or dbg.dtype != torch.int32 or dbg.numel() < 64:
+            raise ValueError("dbg must be an int32 CUDA tensor of at least 64 words on the tensors' device")
+    if k.device != q.device:
+        raise ValueError("q, k and v must live on one device")
+    _check_stream(stream, q.device)
     if sm_scale is None:
         sm_scale = 1.0 / math.sqrt(D)
     if out is None:
         out = torch.empty_like(q)
     else:
-        _require_cuda(out)
-        if out.shape != q.shape or out.dtype != torch.bfloat16:
-            raise ValueError("out must match q")
-    rc = native.lib().fa_fwd_bf16_ex(_ptr(out), _ptr(lse), _ptr(q), _ptr(k), _ptr(v), B, H, H_kv, S, D,
-                                     ctypes.c_float(sm_scale), int(bool(causal)), flags, _ptr(dbg),
-                                     _stream(stream))
+        _check_out(out, q.device, q.shape, torch.bfloat16)
+    with torch.cuda.device(q.device):
+        rc = native.lib().fa_fwd_bf16_ex(_ptr(out), _ptr(lse), _ptr(q), _ptr(k), _ptr(v), B, H, H_kv, S, D,
+                                         ctypes.c_float(sm_scale), int(bool(causal)), flags, _ptr(dbg),
+                                         _stream(stream, q.device))
     native.check(rc)
     return out
 
@@ -86,14 +113,24 @@ def gemm(a: torch.Tensor, bt: torch.Tensor, *, out: Optional[torch.Tensor] = Non
         raise ValueError("gemm takes A[M,K] and Bt[N,K]")
     M, K = a.shape
     N = bt.shape[0]
+    want = torch.float32 if f32_out else torch.bfloat16
+    _check_stream(stream, a.device)
     if out is None:
-        out = torch.empty((M, N), device=a.device, dtype=torch.float32 if f32_out else torch.bfloat16)
+        out = torch.empty((M, N), device=a.device, dtype=want)
+        ldc = N
     else:
-        _require_cuda(out)
-    ldc = out.stride(0)
+        # a row-strided view (columns of a wider buffer) is allowed: ldc carries the pitch
+        if not out.is_cuda or out.device != a.device:
+            raise ValueError(f"out must be a CUDA tensor on {a.device}")
+        if out.dim() != 2 or tuple(out.shape) != (M, N) or out.stride(1) != 1 or out.stride(0) < N:
+            raise ValueError(f"out must be [{M}, {N}] with unit column stride and row pitch >= {N}")
+        if out.dtype != want:
+            raise ValueError(f"out must be {want} (f32_out={f32_out}), not {out.dtype}")
+        ldc = out.stride(0)
     flags = ((native.GEMM_F32_OUT if f32_out else 0) | (native.GEMM_NO_SPLIT if no_split else 0)
              | (native.GEMM_ONE_CTA if one_cta else 0))
-    rc = native.lib().gemm_bf16(_ptr(out), _ptr(a), _ptr(bt), M, N, K, ldc, flags, _stream(stream))
+    with torch.cuda.device(a.device):
+        rc = native.lib().gemm_bf16(_ptr(out), _ptr(a), _ptr(bt), M, N, K, ldc, flags, _stream(stream, a.device))
     native.check(rc)
     return out
 
@@ -113,15 +150,17 @@ def gemm_grouped(a: torch.Tensor, bt: torch.Tensor, *, out: Optional[torch.Tenso
         raise ValueError("gemm_grouped takes A[G,M,K] and Bt[G,N,K]")
     G, M, K = a.shape
     N = bt.shape[1]
+    want = torch.float32 if f32_out else torch.bfloat16
+    _check_stream(stream, a.device)
     if out is None:
-        out = torch.empty((G, M, N), device=a.device, dtype=torch.float32 if f32_out else torch.bfloat16)
+        out = torch.empty((G, M, N), device=a.device, dtype=want)
     else:
-        _require_cuda(out)
-        if tuple(out.shape) != (G, M, N):
-            raise ValueError("out must be [G,M,N]")
+        _check_out(out, a.device, (G, M, N), want)
     flags = ((native.GEMM_F32_OUT if f32_out else 0) | (native.GEMM_NO_SPLIT if no_split else 0)
              | (native.GEMM_ONE_CTA if one_cta else 0))
-    rc = native.lib().gemm_bf16_grouped(_ptr(out), _ptr(a), _ptr(bt), G, M, N, K, N, flags, _stream(stream))
+    with torch.cuda.device(a.device):
+        rc = native.lib().gemm_bf16_grouped(_ptr(out), _ptr(a), _ptr(bt), G, M, N, K, N, flags,
+                                            _stream(stream, a.device))
     native.check(rc)
     return out
 
@@ -134,12 +173,22 @@ def _rowwise_check(x: torch.Tensor, *vecs: torch.Tensor) -> None:
         raise ValueError("weight / bias length must equal N")
 
 
+def _rowwise_out(x, out, stream):
+    _check_stream(stream, x.device)
+    if out is None:
+        return torch.empty_like(x)
+    _check_out(out, x.device, x.shape, torch.float32)
+    return out
+
+
 def softmax(x: torch.Tensor, *, out: Optional[torch.Tensor] = None,
             stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
     """Row-wise softmax of a [rows, N] float32 matrix (test/gpu/softmax.jl:151-163)."""
     _rowwise_check(x)
-    out = torch.empty_like(x) if out is None else out
-    native.check(native.lib().softmax_f32(_ptr(out), _ptr(x), x.shape[0], x.shape[1], _stream(stream)))
+    out = _rowwise_out(x, out, stream)
+    with torch.cuda.device(x.device):
+        rc = native.lib().softmax_f32(_ptr(out), _ptr(x), x.shape[0], x.shape[1], _stream(stream, x.device))
+    native.check(rc)
     return out
 
 
@@ -147,9 +196,11 @@ def rms_norm(x: torch.Tensor, w: torch.Tensor, eps: float = 1e-6, *, out: Option
              stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
     """y = x * w / sqrt(mean(x^2) + eps) per row (test/gpu/rms_norm.jl:121-139)."""
     _rowwise_check(x, w)
-    out = torch.empty_like(x) if out is None else out
-    native.check(native.lib().rms_norm_f32(_ptr(out), _ptr(x), _ptr(w), x.shape[0], x.shape[1],
-                                           ctypes.c_float(eps), _stream(stream)))
+    out = _rowwise_out(x, out, stream)
+    with torch.cuda.device(x.device):
+        rc = native.lib().rms_norm_f32(_ptr(out), _ptr(x), _ptr(w), x.shape[0], x.shape[1],
+                                       ctypes.c_float(eps), _stream(stream, x.device))
+    native.check(rc)
     return out
 
 
@@ -158,9 +209,11 @@ def layer_norm(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor, eps: float 
                stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
     """y = (x - mean) / sqrt(var + eps) * w + bias per row (test/gpu/layer_norm.jl:138-156)."""
     _rowwise_check(x, w, bias)
-    out = torch.empty_like(x) if out is None else out
-    native.check(native.lib().layer_norm_f32(_ptr(out), _ptr(x), _ptr(w), _ptr(bias), x.shape[0],
-                                             x.shape[1], ctypes.c_float(eps), _stream(stream)))
+    out = _rowwise_out(x, out, stream)
+    with torch.cuda.device(x.device):
+        rc = native.lib().layer_norm_f32(_ptr(out), _ptr(x), _ptr(w), _ptr(bias), x.shape[0],
+                                         x.shape[1], ctypes.c_float(eps), _stream(stream, x.device))
+    native.check(rc)
     return out
 
 
@@ -170,8 +223,10 @@ def swiglu(gate: torch.Tensor, up: torch.Tensor, *, out: Optional[torch.Tensor] 
     _require_cuda(gate, up)
     if gate.dtype != torch.float32 or up.dtype != torch.float32 or gate.shape != up.shape:
         raise ValueError("swiglu takes two float32 tensors of one shape")
-    out = torch.empty_like(gate) if out is None else out
-    native.check(native.lib().swiglu_f32(_ptr(out), _ptr(gate), _ptr(up), gate.numel(), _stream(stream)))
+    out = _rowwise_out(gate, out, stream)
+    with torch.cuda.device(gate.device):
+        rc = native.lib().swiglu_f32(_ptr(out), _ptr(gate), _ptr(up), gate.numel(), _stream(stream, gate.device))
+    native.check(rc)
     return out
 
 
@@ -199,6 +254,10 @@ def selftest(which: int, q=None, k=None, v=None, p=None):
 
 
 def sync_status(stream: Optional[torch.cuda.Stream] = None) -> int:
-    """Synchronise and return (and clear) the device status word; 0 = healthy."""
-    s = torch.cuda.current_stream() if stream is None else stream
-    return native.sync_status(s.cuda_stream)
+    """0 = healthy. With a stream: synchronise it and return (and clear) its status word.
+    Without: synchronise the current device and return (and clear) the first nonzero
+    status of ANY stream that launched through the library on it."""
+    if stream is None:
+        return native.device_status()
+    with torch.cuda.device(stream.device):
+        return native.sync_status(stream.cuda_stream)

@@ -272,3 +272,42 @@ def test_gemm_seeded_random_shapes(pkg, gpu, oracle_mod, M, N, K):
     torch.testing.assert_close(c, c_plain, rtol=1e-4, atol=1e-4)
     ref = oracle_mod.gemm_ref_c(bits(a), bits(bt))
     np.testing.assert_allclose(c.cpu().numpy(), ref, rtol=1e-4, atol=1e-4)
+
+
+# ---------------------------------------------------------------------------
+# The full-size GEMM configuration: M = N = K = 8192, entries uniform in [-1, 1], bf16
+# out. The oracle cannot form all of C in test time, so 256 x 256 blocks of C are checked
+# against it over the full K: the four corners, the centre, and blocks drawn from a
+# seeded generator (the reference checks the whole of its small C the same way:
+# test/gpu/blackwell/gemm_highperf_blackwell.jl:224-228, 257-262).
+# ---------------------------------------------------------------------------
+def _c5_blocks(n_random, seed, tiles=8192 // 256):
+    rng = np.random.default_rng(seed)
+    blocks = [(0, 0), (0, tiles - 1), (tiles - 1, 0), (tiles - 1, tiles - 1), (tiles // 2, tiles // 2)]
+    while len(blocks) < 5 + n_random:
+        b = (int(rng.integers(0, tiles)), int(rng.integers(0, tiles)))
+        if b not in blocks:
+            blocks.append(b)
+    return blocks
+
+
+@pytest.mark.parametrize("one_cta", [False, True], ids=["cta_pair", "one_cta"])
+def test_gemm_full_size_uniform_inputs_bf16_out(pkg, gpu, oracle_mod, one_cta):
+    M = N = K = 8192
+    g = torch.Generator().manual_seed(20260005)
+    a = (torch.rand(M, K, generator=g) * 2 - 1).to(torch.bfloat16)
+    bt = (torch.rand(N, K, generator=g) * 2 - 1).to(torch.bfloat16)
+    c = pkg.ops.gemm(a.to(gpu), bt.to(gpu), one_cta=one_cta)
+    status = pkg.ops.sync_status()
+    assert status == 0, pkg.native.strerror(status)
+    assert c.dtype == torch.bfloat16 and tuple(c.shape) == (M, N)
+    a_bits, bt_bits = bits(a), bits(bt)
+    for bi, bj in _c5_blocks(7, 20260005):
+        r0, c0 = bi * 256, bj * 256
+        ref = oracle_mod.gemm_ref_c(a_bits[r0:r0 + 256], bt_bits[c0:c0 + 256])
+        got = c[r0:r0 + 256, c0:c0 + 256].float().cpu().numpy()
+        # one bf16 rounding of the fp32 sum (entries of C are of order sqrt(K) / 3)
+        np.testing.assert_allclose(got, ref, rtol=2 ** -7, atol=2e-3, err_msg=f"block {bi},{bj}")
+    # every element finite, and the whole of C has the spread the inputs imply
+    assert torch.isfinite(c).all()
+    assert 25.0 < float(c.float().std()) < 35.0
