@@ -69,29 +69,6 @@ def attn_flops(B, H, S, D, causal):
     return (2.0 if causal else 4.0) * B * H * S * S * D
 
 
-def measured_peak(region_ms):
-    """bf16 tensor peak to divide by: the pool's measured cuBLAS figure (burst for a
-    short timed region, sustained for one long enough to sit under the power cap)."""
-    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    try:
-        with open(path) as f:
-            mp = json.load(f)
-        if region_ms >= 500.0 and "bf16_tflops_sustained" in mp:
-            return float(mp["bf16_tflops_sustained"]), "measured (sustained cuBLAS bf16)"
-        return float(mp["bf16_tflops"]), "measured (burst cuBLAS bf16)"
-    except Exception:
-        return FALLBACK_PEAK_TFLOPS, "fallback"
-
-
-def measured_hbm_peak():
-    """HBM copy bandwidth to divide by (GB/s): the pool's measured STREAM-style copy."""
-    try:
-        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
-            return float(json.load(f)["hbm_gbs"]), "measured (copy)"
-    except Exception:
-        return FALLBACK_PEAK_GBS, "fallback"
-
-
 def rowwise_cpu(workload, x, w, b):
     """The oracle's float64 restatement of the reference's CPU reference for `workload`."""
     import oracle
@@ -121,16 +98,19 @@ def rowwise_cpu_sample(workload, sample_rows):
 
 
 class ClockSampler(threading.Thread):
-    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+    """Samples the SM clock (every ~0.3 ms) and the throttle reasons (every 8th sample)
+    through NVML for the life of the run; each sample carries its host time, so any timed
+    region can ask for the clocks it saw. Reads only: no GPU setting is changed."""
 
     def __init__(self, index):
         super().__init__(daemon=True)
         self.index = index
-        self.samples = []
-        self.reasons = set()
+        self.t = []          # perf_counter of each sample
+        self.mhz = []
+        self.reason_log = []  # (perf_counter, frozenset of active reasons)
         self.max_mhz = None
+        self.error = None
         self._stop_evt = threading.Event()
-        self.active = False
 
     def run(self):
         try:
@@ -144,23 +124,34 @@ class ClockSampler(threading.Thread):
                 "sw_thermal_slowdown": nv.nvmlClocksEventReasonSwThermalSlowdown,
                 "sw_power_cap": nv.nvmlClocksEventReasonSwPowerCap,
             }
+            i = 0
             while not self._stop_evt.is_set():
-                if self.active:
-                    self.samples.append(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
+                self.mhz.append(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
+                self.t.append(time.perf_counter())
+                if i % 8 == 0:
                     r = nv.nvmlDeviceGetCurrentClocksEventReasons(h)
-                    for k, bit in names.items():
-                        if r & bit:
-                            self.reasons.add(k)
-                time.sleep(0.002)
+                    self.reason_log.append((self.t[-1], frozenset(k for k, bit in names.items() if r & bit)))
+                i += 1
+                time.sleep(0.0003)
         except Exception as e:  # NVML missing: report that instead of inventing numbers
-            self.reasons.add(f"nvml_unavailable:{type(e).__name__}")
+            self.error = f"nvml_unavailable:{type(e).__name__}"
 
     def stop(self):
         self._stop_evt.set()
 
-    def summary(self):
-        return {"sm_mhz": statistics.median(self.samples) if self.samples else None,
-                "sm_max_mhz": self.max_mhz, "samples": len(self.samples), "reasons": sorted(self.reasons)}
+    def window(self, t0, t1):
+        """Clock summary of the samples taken between two perf_counter times."""
+        n = len(self.mhz)     # the lists only grow; read a consistent prefix
+        vals = [self.mhz[i] for i in range(n) if t0 <= self.t[i] <= t1]
+        reasons = set()
+        for t, rs in list(self.reason_log):
+            if t0 <= t <= t1:
+                reasons |= rs
+        if self.error:
+            reasons.add(self.error)
+        return {"sm_mhz": statistics.median(vals) if vals else None,
+                "sm_mhz_min": min(vals) if vals else None, "sm_max_mhz": self.max_mhz,
+                "samples": len(vals), "reasons": sorted(reasons)}
 
 
 def physical_gpu_index(local_rank):
@@ -196,24 +187,6 @@ def bind_to_gpu_local_cpus(index, pci_bus_id=None):
 
 
 # --------------------------------------------------------------------------- CPU arm
-def cpu_sample(workload, n_slices, repeats=1):
-    """Times the CPU oracle (C port of the reference's fab_cpu_ref) on `n_slices`
-    (batch, head) slices of the workload with every host thread. Returns TFLOPS."""
-    import numpy as np
-    import oracle
-    oracle.build_c_oracle()
-    B, H, S, D, causal, sigma, seed = WORKLOADS[workload]
-    rng = np.random.default_rng(seed)
-    q, k, v = (oracle.to_bf16_bits((rng.standard_normal((n_slices, S, D)) * s).astype(np.float32))
-               for s in (sigma, sigma, 1.0))
-    best = float("inf")
-    for _ in range(repeats):
-        t = time.perf_counter()
-        oracle.attention_ref_c(q, k, v, 1.0 / math.sqrt(D), causal, nthreads=host_threads())
-        best = min(best, time.perf_counter() - t)
-    return attn_flops(1, n_slices, S, D, causal) / best / 1e12, best, host_threads()
-
-
 def run_reference_arm(args):
     """The reference's own CPU implementation of the path (its Julia CPU checker
     restated in C: no Julia toolchain exists on these machines), all host threads.
@@ -295,6 +268,161 @@ def run_reference_arm(args):
 
 
 # --------------------------------------------------------------------------- native arm
+def peaks():
+    """(burst bf16 TF/s, sustained bf16 TF/s, HBM GB/s, 'measured' | 'fallback')."""
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            mp = json.load(f)
+        return (float(mp["bf16_tflops"]), float(mp.get("bf16_tflops_sustained", mp["bf16_tflops"])),
+                float(mp["hbm_gbs"]), "measured")
+    except Exception:
+        return FALLBACK_PEAK_TFLOPS, 1400.0, FALLBACK_PEAK_GBS, "fallback"
+
+
+class Problem:
+    """One workload resident on this rank's GPU: inputs, output, the launch, its work."""
+
+    def __init__(self, name, inputs, out, run, work, algo_bytes, text):
+        self.name, self.inputs, self.out, self.run = name, inputs, out, run
+        self.work, self.algo_bytes, self.text = work, algo_bytes, text
+
+
+def attention_problem(ops, dev, name, seed_offset=0):
+    import torch
+    B, H, S, D, causal, sigma, seed = WORKLOADS[name]
+    g = torch.Generator(device=dev).manual_seed(seed + seed_offset)
+    q = (torch.randn(B, H, S, D, device=dev, generator=g) * sigma).to(torch.bfloat16)
+    k = (torch.randn(B, H, S, D, device=dev, generator=g) * sigma).to(torch.bfloat16)
+    v = torch.randn(B, H, S, D, device=dev, generator=g).to(torch.bfloat16)
+    o = torch.empty_like(q)
+    sm_scale = 1.0 / math.sqrt(D)
+
+    def run(ins, out, stream=None):
+        ops.fa_fwd(ins[0], ins[1], ins[2], causal=causal, sm_scale=sm_scale, out=out, stream=stream)
+
+    return Problem(name, [q, k, v], o, run, attn_flops(B, H, S, D, causal), 4 * q.numel() * 2,
+                   f"{name}: B={B} H={H} S={S} D={D} causal={causal}")
+
+
+def attention_shard(pkg, prob, rank, world):
+    """This rank's share of the FIXED problem `prob` split `world` ways by (batch x head):
+    views of its slices (contiguous in [B,H,S,D]), the work they hold and the launch."""
+    q, k, v = prob.inputs
+    B, H, S, D = q.shape
+    b, e = pkg.sharding.attention_shard(B, H, rank, world)
+    flat = [t.view(1, B * H, S, D)[:, b:e] for t in (q, k, v)]
+    out = prob.out.view(1, B * H, S, D)[:, b:e]
+    return flat, out, prob.work * (e - b) / (B * H), e - b
+
+
+def gemm_problem(ops, dev, name, rank):
+    import torch
+    M, N, K, seed = GEMM_WORKLOADS[name]
+    g = torch.Generator(device=dev).manual_seed(seed)
+    a = (torch.rand(M, K, device=dev, generator=g) * 2 - 1).to(torch.bfloat16)
+    g.manual_seed(seed + 1 + rank)
+    bt = (torch.rand(N, K, device=dev, generator=g) * 2 - 1).to(torch.bfloat16)
+    o = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+
+    def run(ins, out, stream=None):
+        ops.gemm(ins[0], ins[1], out=out, stream=stream)
+
+    return Problem(name, [a, bt], o, run, 2.0 * M * N * K, (M * K + N * K + M * N) * 2,
+                   f"{name}: M={M} N={N} K={K} bf16 out")
+
+
+def rowwise_problem(ops, dev, name, rank, rows_override):
+    import torch
+    rows, N, seed = ROWWISE_WORKLOADS[name]
+    rows = rows_override or rows
+    g = torch.Generator(device=dev).manual_seed(seed + rank)
+    x = torch.randn(rows, N, device=dev, generator=g)
+    w = torch.randn(N, device=dev, generator=g) * 0.1 + 1.0
+    bias = torch.randn(N, device=dev, generator=g) * 0.1
+    inputs = [x, torch.randn(rows, N, device=dev, generator=g)] if name == "swiglu" else [x]
+
+    def run(ins, out, stream=None):
+        if name == "softmax":
+            ops.softmax(ins[0], out=out, stream=stream)
+        elif name == "rms_norm":
+            ops.rms_norm(ins[0], w, 1e-6, out=out, stream=stream)
+        elif name == "layer_norm":
+            ops.layer_norm(ins[0], w, bias, 1e-5, out=out, stream=stream)
+        else:
+            ops.swiglu(ins[0], ins[1], out=out, stream=stream)
+
+    nbytes = (len(inputs) + 1) * rows * N * 4
+    return Problem(name, inputs, torch.empty_like(x), run, float(nbytes), nbytes, f"{name}: rows={rows} N={N} fp32")
+
+
+class Bench:
+    """Timing discipline shared by every measurement of the native arm: a time-based
+    warm-up (the reference spins launches for 25 ms before it times, bench/flash_attention.jl:
+    113-127), then `repeats` regions of exactly `steps` back-to-back launches, each bracketed
+    by barrier + synchronize and timed with CUDA events on the launching stream; a region's
+    time is the max over ranks, the reported figure the median over regions."""
+
+    def __init__(self, torch, dist, world, dev, sampler):
+        self.torch, self.dist, self.world, self.dev, self.sampler = torch, dist, world, dev, sampler
+
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
+        self.torch.cuda.synchronize()
+
+    def max_over_ranks(self, x):
+        t = self.torch.tensor([x], dtype=self.torch.float64, device=self.dev)
+        if self.world > 1:
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t[0])
+
+    def warm(self, launch, min_launches, min_ms=25.0):
+        t0, n = time.perf_counter(), 0
+        while n < max(min_launches, 3) or (time.perf_counter() - t0) * 1e3 < min_ms:
+            launch()
+            n += 1
+            if n % 8 == 0:
+                self.torch.cuda.synchronize()   # keep the queue short so the wall clock means something
+        self.torch.cuda.synchronize()
+        return n
+
+    def region(self, launch, steps):
+        """One timed region of exactly `steps` launches: (ms max over ranks, clocks seen)."""
+        torch = self.torch
+        self.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        e0.record()
+        for _ in range(steps):
+            launch()
+        e1.record()
+        self.barrier()
+        t1 = time.perf_counter()
+        return self.max_over_ranks(e0.elapsed_time(e1)), self.sampler.window(t0, t1)
+
+    def measure(self, launch, steps, warmup, repeats=5):
+        n_warm = self.warm(launch, warmup)
+        regions = [self.region(launch, steps) for _ in range(repeats)]
+        ms = sorted(r[0] / steps for r in regions)
+        mid = regions[sorted(range(repeats), key=lambda i: regions[i][0])[repeats // 2]]
+        return {"ms": ms[repeats // 2], "ms_min": ms[0], "ms_max": ms[-1], "repeats": repeats, "steps": steps,
+                "warmup_launches": n_warm, "clocks": mid[1]}
+
+
+def quantisation_note(pkg, name, world, sm):
+    """What the item count alone allows at `world` ranks (a bound, not a measurement)."""
+    if name in GEMM_WORKLOADS:
+        M, N, K, _ = GEMM_WORKLOADS[name]
+        tiles = (M // 256) * ((N // world) // 256)
+        waves = tiles / (sm // 2)
+        return f"{tiles} tiles of 256x256 on {sm // 2} SM pairs = {waves:.2f} waves: at most {waves / math.ceil(waves):.2f} of linear"
+    B, H, S, D, causal, _, _ = WORKLOADS[name]
+    items = (B * H // world) * ((S + 255) // 256)
+    waves = items / sm
+    return (f"{items} items of 256 rows on {sm} SMs = {waves:.2f} rounds: whole items alone allow "
+            f"{waves / math.ceil(waves):.2f} of linear; the last round is cut along the key axis")
+
+
 def run_native_arm(args):
     # stdout carries exactly one line, the JSON record: libraries that write to file
     # descriptor 1 (NCCL prints its version there when a communicator is created) are
@@ -320,115 +448,128 @@ def run_native_arm(args):
         bus = (f"{pr.pci_domain_id:08x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0"
                if hasattr(pr, "pci_bus_id") else None)
         local_cpus = bind_to_gpu_local_cpus(physical_gpu_index(local_rank), bus)
-    if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     pkg = ge.load_package()
     ops = pkg.ops
     pkg.native.lib()   # fail loudly here if the CUDA library is missing
-
-    unit, unit_scale, bound = "TFLOPS", 1e12, "tensor"
-    if args.workload in ROWWISE_WORKLOADS:
-        # this rank's block of rows (world * rows in all): independent rows, no collective
-        rows, N, seed = ROWWISE_WORKLOADS[args.workload]
-        rows = args.rows or rows
-        g = torch.Generator(device=dev).manual_seed(seed + rank)
-        x = torch.randn(rows, N, device=dev, generator=g)
-        w = torch.randn(N, device=dev, generator=g) * 0.1 + 1.0
-        bias = torch.randn(N, device=dev, generator=g) * 0.1
-        o = torch.empty_like(x)
-        if args.workload == "swiglu":
-            inputs = [x, torch.randn(rows, N, device=dev, generator=g)]
-        else:
-            inputs = [x]
-        algo_bytes = (len(inputs) + 1) * rows * N * 4
-        flops_rank = float(algo_bytes)   # the unit of work of this family is the algorithmic byte
-        unit, unit_scale, bound = "GB/s", 1e9, "hbm"
-        metric = f"{args.workload} GB/s (fp32 in, fp32 out, algorithmic bytes), rows={rows} N={N} per GPU"
-        wl_text = f"{args.workload}: rows={rows} N={N} fp32 per GPU, sharded by rows"
-        l2_text = f"input+output {algo_bytes >> 20} MiB per launch > 126 MB L2, no explicit flush"
-        rw_name = args.workload
-
-        def run(ins, out, stream=None):
-            if rw_name == "softmax":
-                ops.softmax(ins[0], out=out, stream=stream)
-            elif rw_name == "rms_norm":
-                ops.rms_norm(ins[0], w, 1e-6, out=out, stream=stream)
-            elif rw_name == "layer_norm":
-                ops.layer_norm(ins[0], w, bias, 1e-5, out=out, stream=stream)
-            else:
-                ops.swiglu(ins[0], ins[1], out=out, stream=stream)
-    elif args.workload in GEMM_WORKLOADS:
-        # C[M, N*world] = A[M,K] B[K, N*world]: A replicated, this rank owns one block of N columns
-        M, N, K, seed = GEMM_WORKLOADS[args.workload]
-        g = torch.Generator(device=dev).manual_seed(seed)
-        a = (torch.rand(M, K, device=dev, generator=g) * 2 - 1).to(torch.bfloat16)
-        g.manual_seed(seed + 1 + rank)
-        bt = (torch.rand(N, K, device=dev, generator=g) * 2 - 1).to(torch.bfloat16)
-        o = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
-        inputs = [a, bt]
-        flops_rank = 2.0 * M * N * K
-        algo_bytes = (M * K + N * K + M * N) * 2
-        metric = "GEMM TFLOPS (bf16 in, fp32 accumulate, bf16 out), M=N=K=8192 per GPU"
-        wl_text = f"{args.workload}: M={M} N={N} K={K} per GPU, C split by column blocks, A replicated"
-        l2_text = "A+B+C 384 MiB per launch > 126 MB L2, no explicit flush"
-
-        def run(ins, out, stream=None):
-            ops.gemm(ins[0], ins[1], out=out, stream=stream)
-    else:
-        B, H, S, D, causal, sigma, seed = WORKLOADS[args.workload]
-        # this rank's shard of the global batch (world * B): B x H slices, generated locally
-        g = torch.Generator(device=dev).manual_seed(seed + rank)
-        q = (torch.randn(B, H, S, D, device=dev, generator=g) * sigma).to(torch.bfloat16)
-        k = (torch.randn(B, H, S, D, device=dev, generator=g) * sigma).to(torch.bfloat16)
-        v = torch.randn(B, H, S, D, device=dev, generator=g).to(torch.bfloat16)
-        o = torch.empty_like(q)
-        inputs = [q, k, v]
-        sm_scale = 1.0 / math.sqrt(D)
-        flops_rank = attn_flops(B, H, S, D, causal)
-        algo_bytes = 4 * q.numel() * 2
-        metric = METRIC if args.workload == "c2" else f"attention fwd TFLOPS (bf16, fp32 accumulate), {args.workload}"
-        wl_text = (f"{args.workload}: B={B} H={H} S={S} D={D} causal={causal} per GPU, sharded by batch*head, "
-                   f"global batch {B * world}")
-        l2_text = f"inputs+output {4 * q.numel() * 2 >> 20} MiB per launch > 126 MB L2, no explicit flush"
-
-        def run(ins, out, stream=None):
-            ops.fa_fwd(ins[0], ins[1], ins[2], causal=causal, sm_scale=sm_scale, out=out, stream=stream)
-
-    def step():
-        run(inputs, o)
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
+    sm_count = torch.cuda.get_device_properties(local_rank).multi_processor_count
+    peak_burst, peak_sustained, peak_hbm, peak_kind = peaks()
 
     sampler = ClockSampler(physical_gpu_index(local_rank))
     sampler.start()
-    for _ in range(max(args.warmup, 3)):
-        step()
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sampler.active = True
-    e0.record()
-    for _ in range(args.steps):
-        step()
-    e1.record()
-    barrier()
-    sampler.active = False
-    status = ops.sync_status()
-    if status != 0:
-        raise SystemExit("device status: " + pkg.native.strerror(status))
-    region_ms = e0.elapsed_time(e1)
-    t = torch.tensor([region_ms], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    region_ms_max = float(t[0])
-    ms_per_step = region_ms_max / args.steps
-    value = flops_rank * world / (ms_per_step * 1e-3) / unit_scale
+    bench = Bench(torch, dist, world, dev, sampler)
+
+    def check_status(where):
+        status = ops.sync_status()
+        if status != 0:
+            raise SystemExit(f"device status after {where}: " + pkg.native.strerror(status))
+
+    # ---- the headline workload: one full configuration per rank ("weak") ----
+    unit, unit_scale, bound = "TFLOPS", 1e12, "tensor"
+    if args.workload in ROWWISE_WORKLOADS:
+        prob = rowwise_problem(ops, dev, args.workload, rank, args.rows)
+        unit, unit_scale, bound = "GB/s", 1e9, "hbm"
+        metric = f"{args.workload} GB/s (fp32 in, fp32 out, algorithmic bytes), {prob.text} per GPU"
+        shard_text = "sharded by rows"
+    elif args.workload in GEMM_WORKLOADS:
+        prob = gemm_problem(ops, dev, args.workload, rank)
+        metric = "GEMM TFLOPS (bf16 in, fp32 accumulate, bf16 out), M=N=K=8192 per GPU"
+        shard_text = "C split by column blocks, A replicated"
+    else:
+        prob = attention_problem(ops, dev, args.workload, seed_offset=rank)
+        metric = METRIC if args.workload == "c2" else f"attention fwd TFLOPS (bf16, fp32 accumulate), {args.workload}"
+        shard_text = f"sharded by batch*head, global batch {WORKLOADS[args.workload][0] * world}"
+    seed = (WORKLOADS.get(args.workload) or GEMM_WORKLOADS.get(args.workload) or ROWWISE_WORKLOADS[args.workload])[-1]
+
+    head = bench.measure(lambda: prob.run(prob.inputs, prob.out), args.steps, args.warmup)
+    check_status("the headline region")
+    ms_per_step = head["ms"]
+    value = prob.work * world / (ms_per_step * 1e-3) / unit_scale
+    achieved = prob.work / (ms_per_step * 1e-3) / unit_scale   # one launch on one GPU
+    region_ms = ms_per_step * args.steps
+    if bound == "tensor":
+        peak = peak_sustained if region_ms >= 500.0 else peak_burst
+        peak_text = f"{peak_kind} ({'sustained' if region_ms >= 500.0 else 'burst'} cuBLAS bf16)"
+    else:
+        peak, peak_text = peak_hbm, f"{peak_kind} (copy)"
+
+    # ---- sustained: one region of at least half a second (power management settles) ----
+    sustained = None
+    if bound == "tensor":
+        n_long = max(args.steps, int(math.ceil(600.0 / ms_per_step)))
+        ms_long, clk_long = bench.region(lambda: prob.run(prob.inputs, prob.out), n_long)
+        check_status("the sustained region")
+        tf_long = prob.work / (ms_long / n_long * 1e-3) / 1e12
+        mhz = clk_long["sm_mhz"]
+        sustained = {"launches": n_long, "region_ms": ms_long, "ms_per_step": ms_long / n_long,
+                     "tflops_per_gpu": tf_long, "peak": peak_sustained,
+                     "frac": tf_long / peak_sustained, "peak_kind": f"{peak_kind} (sustained cuBLAS bf16)",
+                     "clocks": clk_long,
+                     "kcycles_per_launch": (ms_long / n_long) * mhz if mhz else None}
+    head_mhz = head["clocks"]["sm_mhz"]
+
+    # ---- the other configurations, one burst each, and the fixed problems split over the ranks ----
+    configs, strong = {}, {}
+    if args.workload == "c2" and not args.headline_only:
+        for name in ("c2", "c3", "c4", "c5"):
+            is_gemm = name in GEMM_WORKLOADS
+            steps_n = {"c4": 5}.get(name, 20)
+            if name == "c2":
+                full, full_t = prob, head
+            else:
+                full = gemm_problem(ops, dev, name, 0) if is_gemm else attention_problem(ops, dev, name)
+                full_t = bench.measure(lambda: full.run(full.inputs, full.out), steps_n, 3, repeats=3)
+                check_status(f"configs.{name}")
+                tf = full.work / (full_t["ms"] * 1e-3) / 1e12
+                configs[name] = {"workload": full.text, "ms": full_t["ms"], "ms_min": full_t["ms_min"],
+                                 "ms_max": full_t["ms_max"], "tflops": tf, "frac_of_burst_peak": tf / peak_burst,
+                                 "steps": steps_n, "repeats": 3, "sm_mhz": full_t["clocks"]["sm_mhz"],
+                                 "kcycles_per_launch": (full_t["ms"] * full_t["clocks"]["sm_mhz"]
+                                                        if full_t["clocks"]["sm_mhz"] else None)}
+                if name == "c3":
+                    # at D = 64 the exponentials, not the tensor pipe, bound a tile: 16 ex2/clk/SM on the
+                    # MUFU (measured: profiles/ex2_throughput.md) against 2*D flop per score on the tensor pipe
+                    configs[name]["mufu_ceiling_tflops"] = 4.0 * 64 * 16 * sm_count * (full_t["clocks"]["sm_mhz"] or 0) * 1e6 / 1e12
+
+            def shard_launcher(n_ranks, r):
+                if is_gemm:
+                    a, bt = full.inputs
+                    b, e = pkg.sharding.gemm_column_shard(bt.shape[0], r, n_ranks)
+                    bt_s = bt[b:e]
+                    out = torch.empty(a.shape[0], e - b, device=dev, dtype=torch.bfloat16)
+                    return (lambda: full.run([a, bt_s], out)), full.work * (e - b) / bt.shape[0], f"{e - b} of {bt.shape[0]} columns"
+                ins, out, work, n_sl = attention_shard(pkg, full, r, n_ranks)
+                return (lambda: full.run(ins, out)), work, f"{n_sl} of {full.inputs[0].shape[0] * full.inputs[0].shape[1]} (batch, head) slices"
+
+            entry = {"t1_ms": full_t["ms"], "workload": full.text}
+            if world > 1:
+                launch, work, what = shard_launcher(world, rank)
+                t = bench.measure(launch, steps_n, 3, repeats=3)
+                check_status(f"strong.{name}")
+                entry.update({"n": world, "shard_per_rank": what, "ms": t["ms"],
+                              "tflops_total": full.work / (t["ms"] * 1e-3) / 1e12,
+                              "efficiency": full_t["ms"] / (world * t["ms"]),
+                              "bound": quantisation_note(pkg, name, world, sm_count)})
+            else:
+                # one GPU: the shards a rank would hold at 2, 4 and 8 ranks, timed one after the
+                # other (ranks are independent: no collective on the path)
+                emu = {}
+                for n_ranks in (2, 4, 8):
+                    launch, work, what = shard_launcher(n_ranks, 0)
+                    t = bench.measure(launch, steps_n, 3, repeats=3)
+                    emu[str(n_ranks)] = {"shard": what, "ms": t["ms"], "efficiency": full_t["ms"] / (n_ranks * t["ms"])}
+                check_status(f"strong.{name} (emulated)")
+                entry.update({"n": 1, "efficiency": 1.0, "single_gpu_emulation": emu,
+                              "bound_at_8": quantisation_note(pkg, name, 8, sm_count)})
+            strong[name] = entry
+            if name != "c2":
+                del full
+                torch.cuda.empty_cache()
 
     # ---- end to end: host buffers in, host buffer out, copies inside the timed region ----
+    inputs, o = prob.inputs, prob.out
     e2e_steps = max(3, min(args.steps, 10))
-    nbuf = 2
+    nbuf = 3
     h_in = [[torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in inputs] for _ in range(nbuf)]
     h_out = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for _ in range(nbuf)]
     for b in range(nbuf):
@@ -442,8 +583,8 @@ def run_native_arm(args):
     ev_out = [torch.cuda.Event() for _ in range(nbuf)]
 
     def e2e_loop(n):
-        # three streams, two buffer sets: the copy-in of step i+1 and the copy-out of
-        # step i-1 overlap the kernel of step i
+        # three streams, three buffer sets: the copy-in of the next steps and the copy-out of
+        # the previous one overlap the kernel of step i
         for i in range(n):
             b = i % nbuf
             with torch.cuda.stream(s_in):
@@ -454,67 +595,88 @@ def run_native_arm(args):
             with torch.cuda.stream(s_cmp):
                 s_cmp.wait_event(ev_in[b])
                 s_cmp.wait_event(ev_out[b])         # device output of slot b already copied out
-                run(d_in[b], d_out[b], stream=s_cmp)
+                prob.run(d_in[b], d_out[b], stream=s_cmp)
                 ev_cmp[b].record(s_cmp)
             with torch.cuda.stream(s_out):
                 s_out.wait_event(ev_cmp[b])
                 h_out[b].copy_(d_out[b], non_blocking=True)
                 ev_out[b].record(s_out)
 
-    e2e_loop(2)
-    barrier()
+    e2e_loop(nbuf)
+    bench.barrier()
     t0 = time.perf_counter()
     e2e_loop(e2e_steps)
     torch.cuda.synchronize()
-    e2e_ms = (time.perf_counter() - t0) * 1e3
-    t = torch.tensor([e2e_ms], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_ms_step = float(t[0]) / e2e_steps
-    e2e_value = flops_rank * world / (e2e_ms_step * 1e-3) / unit_scale
+    e2e_ms_local = (time.perf_counter() - t0) * 1e3
+    e2e_ms_step = bench.max_over_ranks(e2e_ms_local) / e2e_steps
+    e2e_value = prob.work * world / (e2e_ms_step * 1e-3) / unit_scale
     e2e_ok = bool(torch.equal(h_out[(e2e_steps - 1) % nbuf].to(dev), o))
     h2d_bytes = sum(t.numel() * t.element_size() for t in inputs)
     d2h_bytes = o.numel() * o.element_size()
-    sampler.stop()
-    status = ops.sync_status()
-    if status != 0:
-        raise SystemExit("device status: " + pkg.native.strerror(status))
+    check_status("the end-to-end region")
 
     # verification checksum gathered over ranks (outside every timed region)
     cs = torch.tensor([float(o.float().sum()), float(o.float().abs().sum())], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(cs)
+    sampler.stop()
 
     if rank == 0:
-        peak, peak_kind = measured_peak(region_ms_max) if bound == "tensor" else measured_hbm_peak()
-        achieved = flops_rank / (ms_per_step * 1e-3) / unit_scale   # one launch on one GPU
         line = {
             "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+            "warmup": head["warmup_launches"], "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16" if bound == "tensor" else "f32", "data": "synthetic",
-            "config": {"workload": wl_text, "l2": l2_text,
-                       "seed": seed, "parallelism": f"dp{world} (independent shards, no collective)"},
+            "config": {"workload": f"{prob.text} per GPU, {shard_text}",
+                       "l2": f"inputs+output {prob.algo_bytes >> 20} MiB per launch > 126 MB L2, no explicit flush",
+                       "seed": seed, "parallelism": f"dp{world} (independent shards, no collective)",
+                       "timing": f"warm-up >= 25 ms and >= {max(args.warmup, 3)} launches, then {head['repeats']} regions of "
+                                 f"{args.steps} launches; value = median region, max over ranks"},
             "per_gpu_tflops" if bound == "tensor" else "per_gpu_gbs": value / world,
+            "ms_per_step_min": head["ms_min"], "ms_per_step_max": head["ms_max"], "repeats": head["repeats"],
             "roofline": {"bound": bound, "achieved": achieved, "peak": peak,
                          "unit": "TFLOP/s" if bound == "tensor" else "GB/s",
                          "frac": achieved / peak, "traffic": None if args.rows else NCU_TRAFFIC_BYTES.get(args.workload),
-                         "peak_kind": peak_kind,
-                         "algorithmic_flops_per_launch": flops_rank if bound == "tensor" else None,
-                         "algorithmic_bytes_per_launch": algo_bytes},
+                         "peak_kind": peak_text,
+                         "algorithmic_flops_per_launch": prob.work if bound == "tensor" else None,
+                         "algorithmic_bytes_per_launch": prob.algo_bytes,
+                         "kcycles_per_launch": ms_per_step * head_mhz if head_mhz else None},
             "e2e": {"value": e2e_value, "unit": unit, "h2d_bytes_per_step": h2d_bytes,
                     "d2h_bytes_per_step": d2h_bytes, "ms_per_step": e2e_ms_step, "steps": e2e_steps,
+                    "h2d_gbs_per_rank": h2d_bytes / (e2e_ms_step * 1e-3) / 1e9,
+                    "h2d_gbs_all_ranks": world * h2d_bytes / (e2e_ms_step * 1e-3) / 1e9,
+                    "buffer_sets": nbuf,
                     "matches_resident_run": e2e_ok, "rank0_gpu_local_cpus": local_cpus},
             "gpu_launches": args.steps,
-            "clocks": sampler.summary(),
+            "clocks": head["clocks"],
             "checksum": {"sum": float(cs[0]), "abs_sum": float(cs[1])},
         }
+        if sustained is not None:
+            line["sustained"] = sustained
+        if configs:
+            line["configs"] = configs
+        if strong:
+            line["strong"] = strong
         if world == 1 and not args.no_cpu_baseline and args.workload in WORKLOADS:
+            # the CPU oracle on the first slices of THIS run's inputs: timed as the CPU
+            # baseline, and its output is the spot check of what the GPU wrote
+            import numpy as np
+            import oracle
+            oracle.build_c_oracle()
+            B, H, S, D, causal, _, _ = WORKLOADS[args.workload]
             n_slices = 16
-            cpu_tf, cpu_s, threads = cpu_sample(args.workload, n_slices)
-            line["cpu_baseline"] = {"value": cpu_tf, "unit": "TFLOPS", "cores": threads, "kind": "port",
+            hb = [t.view(B * H, S, D)[:n_slices].cpu().view(torch.int16).numpy().view(np.uint16) for t in inputs]
+            t0 = time.perf_counter()
+            ref = oracle.attention_ref_c(hb[0], hb[1], hb[2], 1.0 / math.sqrt(D), causal, nthreads=host_threads())
+            cpu_s = time.perf_counter() - t0
+            err = np.abs(o.view(B * H, S, D)[:n_slices].float().cpu().numpy() - ref)
+            line["cpu_baseline"] = {"value": attn_flops(1, n_slices, S, D, causal) / cpu_s / 1e12, "unit": "TFLOPS",
+                                    "cores": host_threads(), "kind": "port",
                                     "sample": f"{n_slices} of {B * H} (batch, head) slices of the workload, "
                                               f"{cpu_s:.2f} s wall"}
+            line["oracle_check"] = {"slices": n_slices, "max_abs_err": float(err.max()), "mean_abs_err": float(err.mean()),
+                                    "ok": bool(err.max() <= 2e-2 and err.mean() <= 2e-3)}
         if world == 1 and not args.no_cpu_baseline and args.workload in ROWWISE_WORKLOADS:
+            rows = ROWWISE_WORKLOADS[args.workload][0]
             cpu_gbs, cpu_s = rowwise_cpu_sample(args.workload, 16384)
             line["cpu_baseline"] = {"value": cpu_gbs, "unit": "GB/s", "cores": 1, "kind": "port",
                                     "sample": f"16384 of {rows} rows of the workload, numpy float64, {cpu_s:.2f} s wall"}
@@ -533,6 +695,8 @@ def main():
     ap.add_argument("--workload", choices=sorted(WORKLOADS) + sorted(GEMM_WORKLOADS) + sorted(ROWWISE_WORKLOADS),
                     default="c2")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--headline-only", action="store_true",
+                    help="skip the `configs` and `strong` blocks (the other configurations and the fixed problems split over the ranks)")
     ap.add_argument("--rows", type=int, default=0,
                     help="row-wise workloads only: rows per GPU instead of the default (for small profiler captures)")
     args = ap.parse_args()

@@ -53,6 +53,11 @@ extern "C" {
 #define PTXB200_FA_NO_LAZY_RESCALE 0x1u /* rescale O on every row-max increase (no 2^8 slack) */
 #define PTXB200_FA_SINGLE_BLOCKS 0x2u   /* causal: hand out single 256-row blocks, longest first, instead
                                            of equal-length pairs of blocks (same results bit for bit) */
+#define PTXB200_FA_ALWAYS_TAIL_SPLIT 0x8u /* cut the last round whenever it can be cut, whether or not the
+                                            library expects it to pay (tests, measurements) */
+#define PTXB200_FA_NO_TAIL_SPLIT 0x4u   /* never cut the items of the last, partly filled round along the
+                                           key axis (see "Last round" at fa_fwd_bf16): every output row is
+                                           then one accumulation in key order whatever the SM count */
 
 /* Library version: major*10000 + minor*100 + patch. */
 int ptxb200_version(void);
@@ -161,6 +166,21 @@ int swiglu_f32(void* out, const void* gate, const void* up, long long n, void* s
  * subtracted, P is rounded to bf16 for the second product, O is accumulated in
  * fp32 and rounded once to bf16.
  *
+ * Last round: work is dealt to one persistent CTA per SM in 256-row items, round robin
+ * (the reference's distribution, flash_attention_defs.jl:269-272). When the last round
+ * would leave SMs idle -- items % SMs != 0, most of all when there are fewer items than
+ * SMs -- and cutting pays, the items of that round are cut along the key axis into equal
+ * shares for all SMs; the pieces of an item meet, unnormalised and in fp32, in scratch
+ * that the library keeps per (device, stream) (about 133 KB per SM at D = 128, allocated
+ * with cudaMalloc by the first such launch on a stream -- make it outside stream capture
+ * -- and freed by ptxb200_shutdown; see gemm_bf16 for the table's bound), and the CTA
+ * that holds an item's first keys merges them by the log-sum-exp rule before the one
+ * rounding to bf16. Results stay reproducible from launch to launch on one GPU model;
+ * they differ in the last bits from the uncut key order, which PTXB200_FA_NO_TAIL_SPLIT
+ * keeps. The CTAs of such a launch wait for one another's pieces (bounded, like every
+ * wait here), so they must be able to run at the same time: do not run other work that
+ * occupies the GPU's SMs for seconds concurrently with it.
+ *
  * Replaces the reference's fab_setup launch closure of fab_kernel!
  * (bench/flash_attention.jl:41-85; test/gpu/blackwell/flash_attention_defs.jl:
  * 621-961), which covers D = 128, non-causal only.
@@ -241,6 +261,18 @@ int fa_fwd_bf16_noalloc(void* O, const void* Q, const void* K, const void* V, in
  * array applies: a read that overlaps a launch on another stream races with it.
  */
 int fa_fwd_bf16_noalloc_status(uint32_t* cta_flags_out, int max_flags, void* stream);
+
+/*
+ * The work distribution fa_fwd_bf16 would use for a problem on a GPU with `sm_count`
+ * SMs, computed on the host (no GPU needed; diagnostics and tests). out receives 10 ints
+ * -- 256-row blocks per head, batch*heads, 128-key tiles per head, causal, pairs,
+ * CTAs, units dealt round robin, units of the cut last round, steps of that round,
+ * CTAs sharing it -- then, per CTA of a cut last round, its segment count and 6 ints per
+ * segment (block, batch*head, first tile, end tile, tiles of the item, pieces parked by
+ * following CTAs). Returns the ints written, PTXB200_E_CAPACITY if cap is too small.
+ * The reference's distribution is the round robin of flash_attention_defs.jl:269-272.
+ */
+int ptxb200_fa_plan(int B, int H, int S, int causal, unsigned flags, int sm_count, int* out, int cap);
 
 /*
  * Synchronise `stream`, then return and clear that stream's status word on the

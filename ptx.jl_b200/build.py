@@ -15,7 +15,7 @@ PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libptxb200.so")
 SOURCES = ["api.cu", "gemm_sm100.cu", "gemm2_sm100.cu", "fa_fwd_sm100.cu", "probes_sm100.cu", "rowwise_sm100.cu"]
-HEADERS = ["sm100_prims.cuh", "attn_tiles.cuh", "gemm_epilogue.cuh", "host_common.h"]
+HEADERS = ["sm100_prims.cuh", "attn_tiles.cuh", "attn_sched.cuh", "gemm_epilogue.cuh", "host_common.h"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17",

@@ -98,6 +98,7 @@ struct ScratchEntry {
   int kind = 0;
   void* ptr = nullptr;
   size_t bytes = 0;
+  uint32_t epoch = 0;
   cudaEvent_t done = nullptr;   // recorded behind the last launch that used the buffer
   bool recorded = false;
   unsigned long long last_use = 0;
@@ -138,7 +139,9 @@ int scratch_acquire(const DeviceCtx& ctx, cudaStream_t stream, int kind, size_t 
     free_slot = hit;
     hit = -1;
   }
+  out->fresh = false;
   if (hit < 0) {
+    out->fresh = true;
     if (free_slot < 0) {
       scratch_drop(g_scratch[lru]);
       free_slot = lru;
@@ -160,6 +163,8 @@ int scratch_acquire(const DeviceCtx& ctx, cudaStream_t stream, int kind, size_t 
     hit = free_slot;
   }
   g_scratch[hit].last_use = ++g_scratch_clock;
+  if (++g_scratch[hit].epoch == 0) g_scratch[hit].epoch = 1;
+  out->epoch = g_scratch[hit].epoch;
   out->ptr = g_scratch[hit].ptr;
   out->entry = hit;
   return PTXB200_OK;
@@ -273,7 +278,7 @@ const char* ptxb200_strerror(int code) {
         "fa:mma.o_ready", "fa:softmax.s_full", "fa:corr.alpha", "fa:corr.l_ready",
         "fa:corr.o_done", "probe", "-", "shared memory base not 1024-byte aligned",
         "gemm2:empty", "gemm2:full", "gemm2:acc_empty", "gemm2:acc_full",
-        "fa:softmax.l_free",
+        "fa:softmax.l_free", "fa:corr.combine_piece",
     };
     unsigned site = ((unsigned)code >> 8) & 0xFFu;
     const char* name = site < sizeof(sites) / sizeof(sites[0]) ? sites[site] : "?";
@@ -367,7 +372,8 @@ int fa_fwd_bf16_ex(void* O, void* lse, const void* Q, const void* K, const void*
   if (O == nullptr || Q == nullptr || K == nullptr || V == nullptr) return PTXB200_E_INVALID;
   if (B <= 0 || H <= 0 || H_kv <= 0 || S <= 0 || D <= 0) return PTXB200_E_INVALID;
   if (causal != 0 && causal != 1) return PTXB200_E_INVALID;
-  if (flags & ~(PTXB200_FA_NO_LAZY_RESCALE | PTXB200_FA_SINGLE_BLOCKS)) return PTXB200_E_INVALID;
+  if (flags & ~(PTXB200_FA_NO_LAZY_RESCALE | PTXB200_FA_SINGLE_BLOCKS | PTXB200_FA_NO_TAIL_SPLIT |
+                PTXB200_FA_ALWAYS_TAIL_SPLIT)) return PTXB200_E_INVALID;
   if (!(sm_scale > 0.0f) || !(sm_scale < 1e30f)) return PTXB200_E_INVALID;
   if ((D != 64 && D != 128) || H % H_kv != 0) return PTXB200_E_SHAPE;
   if ((long long)B * H * S >= (1ll << 31)) return PTXB200_E_SHAPE;
@@ -383,6 +389,16 @@ int fa_fwd_bf16_ex(void* O, void* lse, const void* Q, const void* K, const void*
 int fa_fwd_bf16(void* O, const void* Q, const void* K, const void* V, int B, int H, int S, int D,
                 float sm_scale, int causal, unsigned flags, void* dbg, void* stream) {
   return fa_fwd_bf16_ex(O, nullptr, Q, K, V, B, H, H, S, D, sm_scale, causal, flags, dbg, stream);
+}
+
+int ptxb200_fa_plan(int B, int H, int S, int causal, unsigned flags, int sm_count, int* out, int cap) {
+  if (B <= 0 || H <= 0 || S <= 0 || sm_count <= 0 || cap < 0 || (out == nullptr && cap > 0)) return PTXB200_E_INVALID;
+  if (causal != 0 && causal != 1) return PTXB200_E_INVALID;
+  if (flags & ~(PTXB200_FA_NO_LAZY_RESCALE | PTXB200_FA_SINGLE_BLOCKS | PTXB200_FA_NO_TAIL_SPLIT |
+                PTXB200_FA_ALWAYS_TAIL_SPLIT)) return PTXB200_E_INVALID;
+  if ((long long)B * H * S >= (1ll << 31)) return PTXB200_E_SHAPE;
+  const int n = describe_fa_plan(B * H, S, causal, flags, sm_count, out, cap);
+  return n < 0 ? PTXB200_E_CAPACITY : n;
 }
 
 int ptxb200_sync_status(void* stream) {

@@ -48,7 +48,10 @@
 #include <math.h>
 
 #include <mutex>
+#include <utility>
+#include <vector>
 
+#include "attn_sched.cuh"
 #include "attn_tiles.cuh"
 #include "host_common.h"
 
@@ -90,7 +93,7 @@ constexpr int kBatch = PTXB200_FA_BATCH;   // element pairs per exp batch
 enum : uint32_t {
   kSiteLoadQFree = 5, kSiteLoadKvFree = 6, kSiteMmaQFull = 7, kSiteMmaKvFull = 8,
   kSiteMmaPFull = 9, kSiteSoftmaxSFull = 11, kSiteCorrAlpha = 12,
-  kSiteCorrLReady = 13, kSiteCorrODone = 14, kSiteSoftmaxLFree = 22
+  kSiteCorrLReady = 13, kSiteCorrODone = 14, kSiteSoftmaxLFree = 22, kSiteCombinePart = 23
 };
 
 // Timestamp hooks for offline latency studies; compiled out of the product build.
@@ -105,6 +108,17 @@ enum : uint32_t {
   } while (0)
 #else
 #define FA_TSTAMP(cond, rec, tile, ev) do {} while (0)
+#endif
+// Per-CTA wall-clock marks (globaltimer, ns, low 32 bits) into dbg[64 + 4 * cta + k]: kernel
+// entry, roles start, roles done. The caller's dbg buffer must then hold 64 + 4 * grid words.
+// Offline studies only; compiled out of the product build.
+#ifdef PTXB200_FA_CTA_TIMES
+#define FA_CTA_TIME(k)                                                                     \
+  do {                                                                                     \
+    if (threadIdx.x == 256 && p.dbg != nullptr) p.dbg[64 + 4 * blockIdx.x + (k)] = (uint32_t)globaltimer_ns(); \
+  } while (0)
+#else
+#define FA_CTA_TIME(k) do {} while (0)
 #endif
 
 template <int D>
@@ -132,7 +146,8 @@ struct FaCfg {
   static constexpr int kNumBars = kBarLFree + 2;
   static constexpr int kOffTmemSlot = kOffBars + kNumBars * 8;
   static constexpr int kOffAbort = kOffTmemSlot + 8;
-  static constexpr int kSmemBytes = kOffAbort + 8;   // the base must be 1024-byte aligned (checked)
+  static constexpr int kOffSegs = kOffAbort + 8;     // a cut last round: this CTA's segment count, then FaSeg[kTailMaxSegs]
+  static constexpr int kSmemBytes = kOffSegs + 8 + kTailMaxSegs * (int)sizeof(FaSeg);   // the base must be 1024-byte aligned (checked)
   static_assert(kSmemBytes <= 232448, "exceeds the 227 KiB a CTA can opt in to");
   static constexpr uint32_t kColS = 0;                 // + stage * 128
   static constexpr uint32_t kColO = 256;               // + stage * D
@@ -153,7 +168,26 @@ struct FaParams {
   int heads_q;          // query heads per batch entry
   int heads_kv;         // key/value heads per batch entry (divides heads_q)
   int pair_mode;        // causal only: items are dealt out in pairs (see ItemIter)
+  // Launches whose last round is cut along the key axis (the kTail kernels) only:
+  FaSched sched;          // the round-robin part and the cut part of the distribution (attn_sched.cuh)
+  float* parts;           // one slot of parked pieces per CTA
+  uint32_t* part_flags;   // part_flags[c] == epoch once CTA c's slot is complete
+  uint32_t epoch;         // differs from every earlier launch on the same scratch
 };
+
+// One piece of work as the roles see it: key tiles j0 .. j0 + nt[s] - 1 of stage s of item
+// (mb, bh). jlast[s] is the index, relative to j0, of the stage's final tile of the ITEM
+// (the only one that can hold masked keys); it lies outside [0, nt[s]) when this piece does
+// not contain that tile. Without a cut last round every piece is a whole item: j0 = 0,
+// jlast[s] = nt[s] - 1, kind = kWhole.
+struct WorkItem {
+  int mb, bh, j0;
+  int nt[2];
+  int jlast[2];
+  int kind;      // kWhole, kWriter (piece parked in scratch), kCombiner (merges the parked pieces)
+  int n_other;   // kCombiner: pieces parked by the next n_other CTAs
+};
+enum : int { kWhole = 0, kWriter = 1, kCombiner = 2 };
 
 // The work items of one CTA, in order. An item is (m_block, batch*head): 256 query
 // rows of one head.
@@ -174,10 +208,12 @@ struct FaParams {
 template <bool kCausal>
 struct ItemIter {
   int v = 0;   // items this CTA has taken so far
-  __device__ __forceinline__ bool next(const FaParams& p, int& mb, int& bh) {
+  // `units` = how many items (or pairs) are dealt round robin: all of them, or the full
+  // rounds only when the last round is cut
+  __device__ __forceinline__ bool next(const FaParams& p, int& mb, int& bh, const int units) {
     if (!kCausal || !p.pair_mode) {
       const int w = blockIdx.x + v * gridDim.x;
-      if (w >= p.total_work) return false;
+      if (w >= units) return false;
       ++v;
       bh = w / p.num_mblocks;
       // causal without pairing (small launches, where a pair is too coarse a unit):
@@ -188,7 +224,7 @@ struct ItemIter {
     const int pairs_per_head = (p.num_mblocks + 1) >> 1;
     while (true) {
       const int q = blockIdx.x + (v >> 1) * gridDim.x;
-      if (q >= p.bh * pairs_per_head) return false;
+      if (q >= units) return false;
       bh = q / pairs_per_head;
       const int t = q - bh * pairs_per_head;
       const int far = p.num_mblocks - 1 - t;
@@ -216,6 +252,117 @@ __device__ __forceinline__ void tile_counts(const FaParams& p, int mb, int& nt0,
   }
 }
 
+// The pieces of work of one CTA, in order. kTail = false: the whole items ItemIter deals
+// out. kTail = true: the items of the full rounds, then this CTA's segments of the cut last
+// round from the table in shared memory (fa_fwd_kernel's prologue fills it: int count, pad,
+// FaSeg[kTailMaxSegs]).
+template <bool kCausal, bool kTail>
+struct WorkIter {
+  ItemIter<kCausal> rr;
+  int tail_i = -1;   // kTail: -1 while the round-robin part lasts, then the next table entry
+  __device__ __forceinline__ bool next(const FaParams& p, const uint8_t* seg_table, WorkItem& w) {
+    if (!kTail || tail_i < 0) {
+      const int units = kTail ? p.sched.full_units
+                              : ((kCausal && p.pair_mode) ? p.bh * ((p.num_mblocks + 1) >> 1) : p.total_work);
+      if (rr.next(p, w.mb, w.bh, units)) {
+        tile_counts<kCausal>(p, w.mb, w.nt[0], w.nt[1]);
+        w.j0 = 0;
+        w.jlast[0] = w.nt[0] - 1;
+        w.jlast[1] = w.nt[1] - 1;
+        w.kind = kWhole;
+        w.n_other = 0;
+        return true;
+      }
+      if (!kTail) return false;
+      tail_i = 0;
+    }
+    if (tail_i >= *reinterpret_cast<const int*>(seg_table)) return false;
+    const FaSeg g = reinterpret_cast<const FaSeg*>(seg_table + 8)[tail_i];
+    ++tail_i;
+    w.mb = g.mb;
+    w.bh = g.bh;
+    w.j0 = g.j0;
+    int full0, full1;   // the item's tiles per stage
+    tile_counts<kCausal>(p, g.mb, full0, full1);
+    w.nt[0] = min(g.j1, full0) - g.j0;
+    w.nt[1] = g.j1 - g.j0;
+    w.jlast[0] = full0 - 1 - g.j0;
+    w.jlast[1] = full1 - 1 - g.j0;
+    w.kind = g.j0 > 0 ? kWriter : (g.j1 < g.len ? kCombiner : kWhole);
+    w.n_other = g.n_other;
+    return true;
+  }
+  // true while the piece just returned by next() is this CTA's first
+  __device__ __forceinline__ bool on_first() const { return rr.v == 1 || (rr.v == 0 && tail_i == 1); }
+};
+
+// Where a position of the tail line falls, for a whole warp: lane l holds the running
+// step count behind units l, l + 32, ... of the tail (at most 8 per lane), so the unit that
+// contains position x is the number of units that end at or before x, and its start is
+// the largest of those ends.
+struct WarpLocator {
+  int incl[8];
+  __device__ __forceinline__ void operator()(int x, int& u, int& st) const {
+    int cnt = 0, below = 0;
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+      if (incl[k] <= x) {
+        ++cnt;
+        below = max(below, incl[k]);
+      }
+    u = __reduce_add_sync(0xffffffffu, cnt);
+    st = __reduce_max_sync(0xffffffffu, below);
+  }
+};
+
+// One converged warp: this CTA's segments of the tail line into shared memory
+// (int count, pad, FaSeg[kTailMaxSegs]). The host has checked, with the same code, that
+// no CTA of the launch needs more than kTailMaxSegs.
+// Non-causal launches: every unit is one item of nt_all steps, so a position's unit is a division.
+struct UniformLocator {
+  int len;
+  __device__ __forceinline__ void operator()(int x, int& u, int& st) const {
+    u = x / len;
+    st = u * len;
+  }
+};
+
+__device__ __noinline__ void tail_table(const FaSched sc, uint8_t* table) {
+  const int lane = threadIdx.x & 31;
+  if (!sc.causal) {
+    UniformLocator loc{sc.nt_all};
+    FaSeg* segs = reinterpret_cast<FaSeg*>(table + 8);
+    const int n = fa_tail_segments(sc, (int)blockIdx.x, loc, segs);
+    if (lane == 0) *reinterpret_cast<int*>(table) = n < kTailMaxSegs ? n : kTailMaxSegs;
+    __syncwarp();
+    return;
+  }
+  WarpLocator loc;
+  int carry = 0;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const int u = k * 32 + lane;
+    int len = 0;
+    if (u < sc.tail_units) {
+      int la, lb;
+      fa_unit_lens(sc, sc.full_units + u, la, lb);
+      len = la + lb;
+    }
+    int incl = len;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, incl, d);
+      if (lane >= d) incl += t;
+    }
+    loc.incl[k] = u < sc.tail_units ? carry + incl : 0x7fffffff;
+    carry += __shfl_sync(0xffffffffu, incl, 31);
+  }
+  FaSeg* segs = reinterpret_cast<FaSeg*>(table + 8);
+  const int n = fa_tail_segments(sc, (int)blockIdx.x, loc, segs);   // every lane writes the same values
+  if (lane == 0) *reinterpret_cast<int*>(table) = n < kTailMaxSegs ? n : kTailMaxSegs;
+  __syncwarp();
+}
+
 // The MMA-issue thread (one lane of warp 12).
 //
 // Its instruction stream is what paces the tensor pipe: with the ring slot changing
@@ -225,9 +372,9 @@ __device__ __forceinline__ void tile_counts(const FaParams& p, int mb, int& nt0,
 // tile over the slot with every descriptor an immediate (faster in isolation, slower
 // here, most of all for causal shapes), and issuing from the converged warp with an
 // elected lane (the GEMM kernel's scheme).
-template <int D, bool kCausal, bool kConv>
+template <int D, bool kCausal, bool kConv, bool kTail>
 __device__ __forceinline__ void fa_mma_role(const FaParams& p, uint32_t base, uint32_t tmem,
-                                            const WaitCtx& wctx) {
+                                            const WaitCtx& wctx, const uint8_t* seg_table) {
   using C = FaCfg<D>;
   using T = AttnTile<D>;
   constexpr int kSlots = C::kSlots;
@@ -313,17 +460,22 @@ __device__ __forceinline__ void fa_mma_role(const FaParams& p, uint32_t base, ui
   // the MUFU rather than the issue order bounds a tile, this measured slower on causal
   // problems, so there each item starts behind the previous one's last P V.
   constexpr bool kStream = (D == 128);
-  ItemIter<kCausal> items;
-  int mb, bh, nt[2];
-  bool have = items.next(p, mb, bh);
+  WorkIter<kCausal, kTail> items;
+  WorkItem w, w2;
+  int nt[2] = {0, 0};
+  bool have = items.next(p, seg_table, w);
   if (have) {
-    tile_counts<kCausal>(p, mb, nt[0], nt[1]);
+    nt[0] = w.nt[0];
+    nt[1] = w.nt[1];
     start_item(0u, nt);
   }
   while (have) {
-    int mb2, bh2, nt2[2] = {0, 0};
-    const bool have2 = items.next(p, mb2, bh2);
-    if (have2) tile_counts<kCausal>(p, mb2, nt2[0], nt2[1]);
+    int nt2[2] = {0, 0};
+    const bool have2 = items.next(p, seg_table, w2);
+    if (have2) {
+      nt2[0] = w2.nt[0];
+      nt2[1] = w2.nt[1];
+    }
     const bool chain = kStream && have2;
     const uint32_t qph2 = (item_i + 1u) & 1u;
     const int nt_max = nt[1];
@@ -359,7 +511,7 @@ __device__ __forceinline__ void fa_mma_role(const FaParams& p, uint32_t base, ui
       advance(need_k ? 2u : 1u);
     }
     have = have2;
-    mb = mb2; bh = bh2; nt[0] = nt2[0]; nt[1] = nt2[1];
+    nt[0] = nt2[0]; nt[1] = nt2[1];
     ++item_i;
     if (have && !kStream) start_item(item_i & 1u, nt);
   }
@@ -376,7 +528,11 @@ __device__ __forceinline__ void fa_mma_role(const FaParams& p, uint32_t base, ui
 // kRagged (non-causal only): the sequence length is not a multiple of 128, so the last key
 // tile holds keys past the end that must be masked. A variant of its own because the
 // masking code, though it runs once per item, costs the common case 1-2 % when compiled in.
-template <int D, bool kCausal, bool kCtaFlags = false, bool kRagged = false>
+// kTail: the launch's last round of items is cut along the key axis (attn_sched.cuh): the
+// CTA runs its segments of that round after its whole items, parks or merges pieces in the
+// epilogue. A variant of its own so that launches without a cut run exactly the code they
+// ran before the cut existed.
+template <int D, bool kCausal, bool kCtaFlags = false, bool kRagged = false, bool kTail = false>
 __global__ void __launch_bounds__(kThreads, 1)
 fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
               const __grid_constant__ CUtensorMap tmap_v, const FaParams p) {
@@ -401,6 +557,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + C::kOffTmemSlot);
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + C::kOffAbort);
   const WaitCtx wctx{p.status, abort_flag};
+  const uint8_t* seg_table = smem + C::kOffSegs;   // kTail: int count, pad, FaSeg[kTailMaxSegs]
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -430,8 +587,11 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
     tmem_relinquish();
   }
+  FA_CTA_TIME(0);
+  if (kTail && warp == 14) tail_table(p.sched, smem + C::kOffSegs);
   tc_fence_before();
   __syncthreads();
+  FA_CTA_TIME(1);
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
@@ -454,10 +614,10 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
           T::load3(kv_smem + s * T::kTileBytes, tmap, row, slice, bar(C::kBarKvFull + s));
           ++kv_it;
         };
-        ItemIter<kCausal> items;
-        for (int mb, bh; items.next(p, mb, bh); ++item_i) {
-          int nt0, nt1;
-          tile_counts<kCausal>(p, mb, nt0, nt1);
+        WorkIter<kCausal, kTail> items;
+        for (WorkItem w; items.next(p, seg_table, w); ++item_i) {
+          const int mb = w.mb, bh = w.bh, nt1 = w.nt[1];
+          const int kv_row0 = kTail ? w.j0 * kAttnRows : 0;   // first key tile of this piece of the item
           // grouped heads: query head h reads key/value head h / (heads_q / heads_kv)
           const int b_idx = bh / p.heads_q;
           const int kv_head = (bh - b_idx * p.heads_q) / (p.heads_q / p.heads_kv);
@@ -467,24 +627,24 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
           mbar_wait(bar(C::kBarQFree + 0), (item_i & 1u) ^ 1u, wctx, kSiteLoadQFree);
           mbar_arrive_expect_tx(bar(C::kBarQFull + 0), T::kTileBytes);
           T::load3(q_smem, &tmap_q, q_row0, bh, bar(C::kBarQFull + 0));
-          kv_load(&tmap_k, 0, kv_slice);
+          kv_load(&tmap_k, kv_row0, kv_slice);
           mbar_wait(bar(C::kBarQFree + 1), (item_i & 1u) ^ 1u, wctx, kSiteLoadQFree);
           mbar_arrive_expect_tx(bar(C::kBarQFull + 1), T::kTileBytes);
           T::load3(q_smem + T::kTileBytes, &tmap_q, q_row0 + kAttnRows, bh, bar(C::kBarQFull + 1));
           for (int j = 0; j < nt1; ++j) {
             FA_TSTAMP(blockIdx.x == 0 && items.on_first(), 3, j, 0);
-            kv_load(&tmap_v, j * kAttnRows, kv_slice);
+            kv_load(&tmap_v, kv_row0 + j * kAttnRows, kv_slice);
             FA_TSTAMP(blockIdx.x == 0 && items.on_first(), 3, j, 1);
-            if (j + 1 < nt1) kv_load(&tmap_k, (j + 1) * kAttnRows, kv_slice);
+            if (j + 1 < nt1) kv_load(&tmap_k, kv_row0 + (j + 1) * kAttnRows, kv_slice);
           }
         }
         if (p.dbg != nullptr && blockIdx.x == 0) p.dbg[0] = kv_it;
       }
     } else if (warp == 12) {
 #ifdef PTXB200_FA_MMA_CONVERGED
-      fa_mma_role<D, kCausal, true>(p, base, tmem, wctx);
+      fa_mma_role<D, kCausal, true, kTail>(p, base, tmem, wctx, seg_table);
 #else
-      if (elect_one()) fa_mma_role<D, kCausal, false>(p, base, tmem, wctx);
+      if (elect_one()) fa_mma_role<D, kCausal, false, kTail>(p, base, tmem, wctx, seg_table);
 #endif
     }
   } else if (warp < 8) {
@@ -498,12 +658,13 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
     const uint32_t t_row = tmem_addr(tmem, (warp & 3) * 32, C::kColS + stage * 128);
     const float scale_log2 = p.scale_log2;
     uint32_t cnt_s = 0, items_done = 0;
-    ItemIter<kCausal> items;
-    for (int mb, bh; items.next(p, mb, bh);) {
-      int nt[2];
-      tile_counts<kCausal>(p, mb, nt[0], nt[1]);
-      const int ntiles = nt[stage];
-      [[maybe_unused]] const int kv_tail = p.seqlen - (ntiles - 1) * kAttnRows;   // keys in the last tile (non-causal)
+    WorkIter<kCausal, kTail> items;
+    for (WorkItem w; items.next(p, seg_table, w);) {
+      const int ntiles = stage ? w.nt[1] : w.nt[0];
+      // the stage's final tile of the item: the piece's last tile, unless the item is cut there
+      const int jlast = kTail ? (stage ? w.jlast[1] : w.jlast[0]) : ntiles - 1;
+      [[maybe_unused]] const int kv_tail =   // keys in the sequence's last tile (non-causal)
+          p.seqlen - ((kTail ? (p.seqlen + kAttnRows - 1) / kAttnRows : ntiles) - 1) * kAttnRows;
       [[maybe_unused]] const bool stamp = blockIdx.x == 0 && items.on_first() && row == 0;
       float m_run = -INFINITY;
       float l_run = 0.0f;
@@ -521,7 +682,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
         for (int c = 0; c < 4; ++c) tc_wait_ld_bind(v[c]);
         FA_TSTAMP(stamp, stage, j, 2);
 
-        if (kCausal && j == ntiles - 1) {
+        if (kCausal && j == jlast) {
           // diagonal tile: key (local) column i is kept iff i <= row (keys past the end of
           // the sequence lie beyond every valid row's diagonal)
 #pragma unroll
@@ -530,7 +691,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
             for (int i = 0; i < 32; ++i)
               if (c * 32 + i > row) v[c][i] = 0xFF800000u;  // -inf
         }
-        if (kRagged && !kCausal && j == ntiles - 1 && kv_tail < kAttnRows) {
+        if (kRagged && !kCausal && j == jlast && kv_tail < kAttnRows) {
           // last tile of a sequence that is not a multiple of 128: its keys past the end
           // loaded as zeros and must not count
 #pragma unroll
@@ -634,10 +795,10 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
     uint32_t cnt_a[2] = {0, 0};
     uint32_t cnt_h[2] = {0, 0};   // S tiles seen per stage
     uint32_t item_i = 0;
-    ItemIter<kCausal> items;
-    for (int mb, bh; items.next(p, mb, bh); ++item_i) {
-      int nt[2];
-      tile_counts<kCausal>(p, mb, nt[0], nt[1]);
+    WorkIter<kCausal, kTail> items;
+    for (WorkItem w; items.next(p, seg_table, w); ++item_i) {
+      const int mb = w.mb, bh = w.bh;
+      const int nt[2] = {w.nt[0], w.nt[1]};
       const int nt_max = nt[1];
       float l_part[2] = {0.0f, 0.0f};   // row sums of the columns this thread exponentiates
       float neg_prev[2] = {0.0f, 0.0f};
@@ -650,8 +811,10 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
             // Only a stage's last tile can hold masked keys: those above the diagonal
             // (causal) or past the end of the sequence (non-causal, S % 128 != 0). `keep`
             // is the last key column this row keeps there.
-            const bool mask_tile = j == nt[s] - 1 && (kCausal || (kRagged && p.seqlen - j * kAttnRows < kAttnRows));
-            const int keep = kCausal ? row : p.seqlen - j * kAttnRows - 1;
+            const int j_abs = kTail ? w.j0 + j : j;   // the tile's index within the head's sequence
+            const bool mask_tile = j == (kTail ? w.jlast[s] : nt[s] - 1) &&
+                                   (kCausal || (kRagged && p.seqlen - j_abs * kAttnRows < kAttnRows));
+            const int keep = kCausal ? row : p.seqlen - j_abs * kAttnRows - 1;
             {
               // fetch this row's last 32 scores while the softmax warp forms the maximum
               mbar_wait(bar(C::kBarSFull + s), cnt_h[s] & 1u, wctx, kSiteSoftmaxSFull);
@@ -715,41 +878,149 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
           }
         }
       }
-      // ---- epilogue: O / l -> bf16 -> global ----
-      const int q_row0 = bh * p.seqlen + mb * 2 * kAttnRows;
-#pragma unroll
-      for (int s = 0; s < 2; ++s) {
-        // rows past the end of the sequence were computed on zero-filled queries: not written
-        const bool row_valid = mb * 2 * kAttnRows + s * kAttnRows + row < p.seqlen;
-        mbar_wait(bar(C::kBarODone + s), item_i & 1u, wctx, kSiteCorrODone);
-        mbar_wait(bar(C::kBarLReady + s), item_i & 1u, wctx, kSiteCorrLReady);
-        tc_fence_after();
-        const float l_total = stats_l[s * 128 + row] + l_part[s];
-        mbar_arrive(bar(C::kBarLFree + s));   // the softmax warps may publish the next item's sum
-        const float inv_l = 1.0f / l_total;
-        if (p.lse != nullptr && row_valid) {
-          // sum_j 2^(s_j c) = 2^(m c) * l with basis -m c in neg_prev: natural log of it
-          p.lse[q_row0 + s * kAttnRows + row] = (log2f(l_total) - neg_prev[s]) * 0.6931471805599453f;
+      if constexpr (!kTail) {
+        // ---- epilogue: O / l -> bf16 -> global ----
+        const int q_row0 = bh * p.seqlen + mb * 2 * kAttnRows;
+  #pragma unroll
+        for (int s = 0; s < 2; ++s) {
+          // rows past the end of the sequence were computed on zero-filled queries: not written
+          const bool row_valid = mb * 2 * kAttnRows + s * kAttnRows + row < p.seqlen;
+          mbar_wait(bar(C::kBarODone + s), item_i & 1u, wctx, kSiteCorrODone);
+          mbar_wait(bar(C::kBarLReady + s), item_i & 1u, wctx, kSiteCorrLReady);
+          tc_fence_after();
+          const float l_total = stats_l[s * 128 + row] + l_part[s];
+          mbar_arrive(bar(C::kBarLFree + s));   // the softmax warps may publish the next item's sum
+          const float inv_l = 1.0f / l_total;
+          if (p.lse != nullptr && row_valid) {
+            // sum_j 2^(s_j c) = 2^(m c) * l with basis -m c in neg_prev: natural log of it
+            p.lse[q_row0 + s * kAttnRows + row] = (log2f(l_total) - neg_prev[s]) * 0.6931471805599453f;
+          }
+          __nv_bfloat16* dst = p.o + (size_t)(q_row0 + s * kAttnRows + row) * D;
+  #pragma unroll 1
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t o[32];
+            tmem_ld32(t_lane + C::kColO + s * D + c * 32, o);
+            tc_wait_ld_bind(o);
+            if (c == D / 32 - 1) {
+              // last read of O_s: the next item may overwrite it
+              tc_fence_before();
+              mbar_arrive(bar(C::kBarPFull + 2 * s));
+            }
+  #pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const uint32_t p0 = pack_bf16x2(__uint_as_float(o[8 * i + 0]) * inv_l, __uint_as_float(o[8 * i + 1]) * inv_l);
+              const uint32_t p1 = pack_bf16x2(__uint_as_float(o[8 * i + 2]) * inv_l, __uint_as_float(o[8 * i + 3]) * inv_l);
+              const uint32_t p2 = pack_bf16x2(__uint_as_float(o[8 * i + 4]) * inv_l, __uint_as_float(o[8 * i + 5]) * inv_l);
+              const uint32_t p3 = pack_bf16x2(__uint_as_float(o[8 * i + 6]) * inv_l, __uint_as_float(o[8 * i + 7]) * inv_l);
+              if (row_valid) st_global_v4(dst + c * 32 + 8 * i, p0, p1, p2, p3);
+            }
+          }
         }
-        __nv_bfloat16* dst = p.o + (size_t)(q_row0 + s * kAttnRows + row) * D;
-#pragma unroll 1
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t o[32];
-          tmem_ld32(t_lane + C::kColO + s * D + c * 32, o);
-          tc_wait_ld_bind(o);
-          if (c == D / 32 - 1) {
-            // last read of O_s: the next item may overwrite it
-            tc_fence_before();
-            mbar_arrive(bar(C::kBarPFull + 2 * s));
+      } else {
+        // A piece of an item cut along the key axis is either parked in this CTA's scratch
+        // slot, unnormalised -- fp32 O, row sum l and basis b with O = sum_j 2^(s_j c - b) v_j
+        // -- or, in the CTA that holds the item's first keys, merged with the pieces the
+        // following CTAs parked:
+        //   B = max_p b_p,  O = sum_p 2^(b_p - B) O_p,  l = sum_p 2^(b_p - B) l_p,  out = O / l.
+        const int q_row0 = bh * p.seqlen + mb * 2 * kAttnRows;
+        constexpr int kStageFloats = 256 + kAttnRows * D;   // l[128], b[128], O as [D/4][128 rows][4]
+        float* const my_slot = p.parts + (size_t)blockIdx.x * (2 * kStageFloats);
+        if (w.kind == kCombiner) {
+          // the other pieces are complete once their CTAs' flags carry this launch's epoch
+          for (int k = 1; k <= w.n_other; ++k)
+            flag_wait(p.part_flags + blockIdx.x + k, p.epoch, wctx, kSiteCombinePart);
+        }
+  #pragma unroll
+        for (int s = 0; s < 2; ++s) {
+          // rows past the end of the sequence were computed on zero-filled queries: not written
+          const bool row_valid = mb * 2 * kAttnRows + s * kAttnRows + row < p.seqlen;
+          mbar_wait(bar(C::kBarODone + s), item_i & 1u, wctx, kSiteCorrODone);
+          mbar_wait(bar(C::kBarLReady + s), item_i & 1u, wctx, kSiteCorrLReady);
+          tc_fence_after();
+          float l_total = stats_l[s * 128 + row] + l_part[s];
+          mbar_arrive(bar(C::kBarLFree + s));   // the softmax warps may publish the next item's sum
+          if (w.kind == kWriter) {
+            float* const dst = my_slot + s * kStageFloats;
+            dst[row] = l_total;
+            dst[128 + row] = -neg_prev[s];
+  #pragma unroll 1
+            for (int c = 0; c < D / 32; ++c) {
+              uint32_t o[32];
+              tmem_ld32(t_lane + C::kColO + s * D + c * 32, o);
+              tc_wait_ld_bind(o);
+              if (c == D / 32 - 1) {
+                // last read of O_s: the next item may overwrite it
+                tc_fence_before();
+                mbar_arrive(bar(C::kBarPFull + 2 * s));
+              }
+  #pragma unroll
+              for (int i = 0; i < 8; ++i)
+                st_global_v4(dst + 256 + ((c * 8 + i) * kAttnRows + row) * 4, o[4 * i], o[4 * i + 1], o[4 * i + 2],
+                             o[4 * i + 3]);
+            }
+            continue;
           }
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const uint32_t p0 = pack_bf16x2(__uint_as_float(o[8 * i + 0]) * inv_l, __uint_as_float(o[8 * i + 1]) * inv_l);
-            const uint32_t p1 = pack_bf16x2(__uint_as_float(o[8 * i + 2]) * inv_l, __uint_as_float(o[8 * i + 3]) * inv_l);
-            const uint32_t p2 = pack_bf16x2(__uint_as_float(o[8 * i + 4]) * inv_l, __uint_as_float(o[8 * i + 5]) * inv_l);
-            const uint32_t p3 = pack_bf16x2(__uint_as_float(o[8 * i + 6]) * inv_l, __uint_as_float(o[8 * i + 7]) * inv_l);
-            if (row_valid) st_global_v4(dst + c * 32 + 8 * i, p0, p1, p2, p3);
+          float basis = -neg_prev[s];   // log2 basis of this CTA's O and l
+          float w_own = 1.0f;
+          if (w.kind == kCombiner) {
+            const float b_own = basis;
+            for (int k = 1; k <= w.n_other; ++k)
+              basis = fmaxf(basis, __ldcg(my_slot + (size_t)k * (2 * kStageFloats) + s * kStageFloats + 128 + row));
+            w_own = ex2_approx(b_own - basis);
+            l_total *= w_own;
+            for (int k = 1; k <= w.n_other; ++k) {
+              const float* src = my_slot + (size_t)k * (2 * kStageFloats) + s * kStageFloats;
+              l_total += __ldcg(src + row) * ex2_approx(__ldcg(src + 128 + row) - basis);
+            }
           }
+          const float inv_l = 1.0f / l_total;
+          if (p.lse != nullptr && row_valid) {
+            // sum_j 2^(s_j c) = 2^b * l with b the basis: natural log of it
+            p.lse[q_row0 + s * kAttnRows + row] = (log2f(l_total) + basis) * 0.6931471805599453f;
+          }
+          __nv_bfloat16* dst = p.o + (size_t)(q_row0 + s * kAttnRows + row) * D;
+  #pragma unroll 1
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t o[32];
+            tmem_ld32(t_lane + C::kColO + s * D + c * 32, o);
+            tc_wait_ld_bind(o);
+            if (c == D / 32 - 1) {
+              // last read of O_s: the next item may overwrite it
+              tc_fence_before();
+              mbar_arrive(bar(C::kBarPFull + 2 * s));
+            }
+            if (w.kind == kCombiner) {
+  #pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * w_own);
+  #pragma unroll 1
+              for (int k = 1; k <= w.n_other; ++k) {
+                const float* src = my_slot + (size_t)k * (2 * kStageFloats) + s * kStageFloats;
+                const float wk = ex2_approx(__ldcg(src + 128 + row) - basis);
+  #pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  const float4 part = __ldcg(reinterpret_cast<const float4*>(src + 256 + ((c * 8 + i) * kAttnRows + row) * 4));
+                  o[4 * i + 0] = __float_as_uint(fmaf(part.x, wk, __uint_as_float(o[4 * i + 0])));
+                  o[4 * i + 1] = __float_as_uint(fmaf(part.y, wk, __uint_as_float(o[4 * i + 1])));
+                  o[4 * i + 2] = __float_as_uint(fmaf(part.z, wk, __uint_as_float(o[4 * i + 2])));
+                  o[4 * i + 3] = __float_as_uint(fmaf(part.w, wk, __uint_as_float(o[4 * i + 3])));
+                }
+              }
+            }
+  #pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const uint32_t p0 = pack_bf16x2(__uint_as_float(o[8 * i + 0]) * inv_l, __uint_as_float(o[8 * i + 1]) * inv_l);
+              const uint32_t p1 = pack_bf16x2(__uint_as_float(o[8 * i + 2]) * inv_l, __uint_as_float(o[8 * i + 3]) * inv_l);
+              const uint32_t p2 = pack_bf16x2(__uint_as_float(o[8 * i + 4]) * inv_l, __uint_as_float(o[8 * i + 5]) * inv_l);
+              const uint32_t p3 = pack_bf16x2(__uint_as_float(o[8 * i + 6]) * inv_l, __uint_as_float(o[8 * i + 7]) * inv_l);
+              if (row_valid) st_global_v4(dst + c * 32 + 8 * i, p0, p1, p2, p3);
+            }
+          }
+        }
+        if (w.kind == kWriter) {
+          // both stages of the piece are in the slot: make them visible, then raise the flag
+          __threadfence();
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (row == 0) st_release_gpu(p.part_flags + blockIdx.x, p.epoch);
         }
       }
     }
@@ -762,6 +1033,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
 
   tc_fence_before();
   __syncthreads();
+  FA_CTA_TIME(3);
   if (warp == 12) {
     tc_fence_after();
     tmem_dealloc(tmem, 512);
@@ -802,6 +1074,129 @@ int causal_pair_mode(int bh, int nmb, int nt_all, int sm_count) {
   return worst_p * 10 <= worst_i * 11 ? 1 : 0;
 }
 
+// ---------------------------------------------------------------------------
+// Choosing the distribution of a launch (host)
+// ---------------------------------------------------------------------------
+struct HostLocator {   // the tail line's unit starts as a plain array
+  const int* starts;   // starts[u] = first step of tail unit u; starts[n] = one past the end
+  int n;
+  __host__ __device__ void operator()(int x, int& u, int& st) const {
+    int lo = 0, hi = n;   // starts[lo] <= x < starts[hi]
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) / 2;
+      if (starts[mid] <= x) lo = mid; else hi = mid;
+    }
+    u = lo;
+    st = starts[lo];
+  }
+};
+
+// Steps the busiest CTA runs when units [0, units) are dealt round robin to `grid` CTAs.
+long long worst_round_robin(const FaSched& sc, int units, int grid) {
+  long long worst = 0;
+  for (int c = 0; c < grid; ++c) {
+    long long sum = 0;
+    for (int q = c; q < units; q += grid) {
+      int la, lb;
+      fa_unit_lens(sc, q, la, lb);
+      sum += la + lb;
+    }
+    worst = sum > worst ? sum : worst;
+  }
+  return worst;
+}
+
+constexpr int kSplitOverheadSteps = 3;   // what a second segment, parking and merging cost a CTA, in steps (measured: 2.5-3)
+constexpr int kSplitMaxRounds = 64;      // beyond this many full rounds the tail is noise: not split
+
+// Round robin over whole units (the reference's distribution), or the same with the last,
+// partly filled round cut along the key axis when that shortens the busiest CTA's work by
+// more than the overhead of the cut.
+FaSched plan_schedule(int bh, int nmb, int nt_all, int causal, unsigned flags, int sm_count, bool may_split) {
+  FaSched legacy;
+  legacy.num_mblocks = nmb;
+  legacy.bh = bh;
+  legacy.nt_all = nt_all;
+  legacy.causal = causal;
+  legacy.pair_mode = (causal && !(flags & PTXB200_FA_SINGLE_BLOCKS)) ? causal_pair_mode(bh, nmb, nt_all, sm_count) : 0;
+  const long long legacy_units = (long long)bh * (legacy.pair_mode ? (nmb + 1) / 2 : nmb);
+  legacy.grid = legacy_units < sm_count ? (int)legacy_units : sm_count;
+  legacy.full_units = (int)legacy_units;
+  legacy.tail_units = legacy.tail_steps = legacy.tail_ctas = 0;
+  if (!may_split || (flags & PTXB200_FA_NO_TAIL_SPLIT) || sm_count > 256) return legacy;
+
+  struct Key {
+    int bh, nmb, nt_all, causal, sm;
+    unsigned flags;
+    bool operator==(const Key& o) const {
+      return bh == o.bh && nmb == o.nmb && nt_all == o.nt_all && causal == o.causal && sm == o.sm && flags == o.flags;
+    }
+  };
+  static std::mutex mu;
+  static std::vector<std::pair<Key, FaSched>> cache;   // the last few shapes: the decision walks every tail CTA
+  const Key key{bh, nmb, nt_all, causal, sm_count, flags};
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    for (const auto& kv : cache)
+      if (kv.first == key) return kv.second;
+  }
+  auto remember = [&](const FaSched& sc) {
+    std::lock_guard<std::mutex> lock(mu);
+    if (cache.size() >= 16) cache.erase(cache.begin());
+    cache.emplace_back(key, sc);
+    return sc;
+  };
+
+  FaSched sc = legacy;
+  sc.pair_mode = (causal && !(flags & PTXB200_FA_SINGLE_BLOCKS)) ? 1 : 0;   // pairs keep a head's CTAs together; the cut balances them
+  const long long units = (long long)bh * (sc.pair_mode ? (nmb + 1) / 2 : nmb);
+  if (units > (long long)kSplitMaxRounds * sm_count) return remember(legacy);
+  sc.grid = sm_count;
+  sc.full_units = (int)(units / sm_count) * sm_count;
+  sc.tail_units = (int)units - sc.full_units;
+  if (sc.tail_units == 0) return remember(legacy);
+  std::vector<int> starts(sc.tail_units + 1, 0);
+  int longest_item = 0;
+  for (int u = 0; u < sc.tail_units; ++u) {
+    int la, lb;
+    fa_unit_lens(sc, sc.full_units + u, la, lb);
+    starts[u + 1] = starts[u] + la + lb;
+    longest_item = la > longest_item ? la : longest_item;
+    longest_item = lb > longest_item ? lb : longest_item;
+  }
+  sc.tail_steps = starts.back();
+  if ((long long)sc.tail_steps * (sm_count + 1) >= (1ll << 31)) return remember(legacy);   // cut positions are 32-bit products
+  int span_min = (longest_item + kTailMaxParts - 3) / (kTailMaxParts - 2);   // at most kTailMaxParts pieces per item
+  if (span_min < 2 * fa_min_seg(causal)) span_min = 2 * fa_min_seg(causal);
+  sc.tail_ctas = sc.tail_steps / span_min < sm_count ? sc.tail_steps / span_min : sm_count;
+  if (sc.tail_ctas < 2) return remember(legacy);
+  // the kernel's per-CTA table and the combiner's reads are bounded: walk every tail CTA,
+  // and take the busiest one's steps from the walk (cuts snap to item edges, so spans differ)
+  HostLocator loc{starts.data(), (int)starts.size() - 1};
+  int tail_worst = 0;
+  for (int c = 0; c < sc.tail_ctas; ++c) {
+    FaSeg segs[kTailMaxSegs];
+    const int n = fa_tail_segments(sc, c, loc, segs);
+    if (n > kTailMaxSegs) return remember(legacy);
+    int steps = 0;
+    for (int i = 0; i < n; ++i) {
+      if (segs[i].n_other + 1 > kTailMaxParts) return remember(legacy);
+      steps += segs[i].j1 - segs[i].j0;
+    }
+    tail_worst = steps > tail_worst ? steps : tail_worst;
+  }
+  const long long split_worst = worst_round_robin(sc, sc.full_units, sc.grid) + tail_worst + kSplitOverheadSteps;
+  const long long legacy_worst = worst_round_robin(legacy, legacy.full_units, legacy.grid);
+  if (!(flags & PTXB200_FA_ALWAYS_TAIL_SPLIT) && split_worst * 100 > legacy_worst * 92)
+    return remember(legacy);   // cut only for a gain of a twelfth or more
+  return remember(sc);
+}
+
+constexpr size_t kPartsHeaderBytes = 4096;   // one flag word per CTA, ahead of the slots
+
+template <int D>
+constexpr size_t parts_slot_bytes() { return (size_t)2 * (256 + kAttnRows * D) * sizeof(float); }
+
 template <int D, bool kCausal>
 int launch_variant(const DeviceCtx& ctx, const CUtensorMap& tq, const CUtensorMap& tk,
                    const CUtensorMap& tv, const FaParams& p, cudaStream_t stream) {
@@ -811,34 +1206,44 @@ int launch_variant(const DeviceCtx& ctx, const CUtensorMap& tq, const CUtensorMa
     PTXB200_CUDA_TRY(cudaFuncSetAttribute(fa_fwd_kernel<D, kCausal>,
                                           cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           C::kSmemBytes));
-    if (!kCausal)
+    PTXB200_CUDA_TRY(cudaFuncSetAttribute(fa_fwd_kernel<D, kCausal, false, false, true>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          C::kSmemBytes));
+    if (!kCausal) {
       PTXB200_CUDA_TRY(cudaFuncSetAttribute(fa_fwd_kernel<D, false, false, true>,
                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
                                             C::kSmemBytes));
+      PTXB200_CUDA_TRY(cudaFuncSetAttribute(fa_fwd_kernel<D, false, false, true, true>,
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            C::kSmemBytes));
+    }
     return PTXB200_OK;
   });
   if (rc != PTXB200_OK) return rc;
-  const int units = (kCausal && p.pair_mode) ? p.bh * ((p.num_mblocks + 1) / 2) : p.total_work;   // what ItemIter deals out
-  const int grid = units < ctx.sm_count ? units : ctx.sm_count;
-  if (!kCausal && p.seqlen % kAttnRows != 0)
-    fa_fwd_kernel<D, false, false, true><<<grid, kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, p);
-  else
-    fa_fwd_kernel<D, kCausal><<<grid, kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, p);
+  const bool ragged = !kCausal && p.seqlen % kAttnRows != 0;
+  if (p.sched.tail_units > 0) {
+    // the last round is cut: every SM gets a CTA
+    const int grid = p.sched.grid;
+    if (ragged)
+      fa_fwd_kernel<D, false, false, true, true><<<grid, kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, p);
+    else
+      fa_fwd_kernel<D, kCausal, false, false, true><<<grid, kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, p);
+  } else {
+    const int units = (kCausal && p.pair_mode) ? p.bh * ((p.num_mblocks + 1) / 2) : p.total_work;   // what ItemIter deals out
+    const int grid = units < ctx.sm_count ? units : ctx.sm_count;
+    if (ragged)
+      fa_fwd_kernel<D, false, false, true><<<grid, kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, p);
+    else
+      fa_fwd_kernel<D, kCausal><<<grid, kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, p);
+  }
   PTXB200_CUDA_TRY(cudaGetLastError());
   return PTXB200_OK;
 }
 
-}  // namespace
-
-int launch_fa_fwd(const DeviceCtx& ctx, void* O, void* lse, const void* Q, const void* K,
-                  const void* V, int B, int H, int H_kv, int S, int D, float sm_scale, int causal,
-                  unsigned flags, void* dbg, uint32_t* status, cudaStream_t stream) {
-  CUtensorMap tq, tk, tv;
-  int rc;
-  if ((rc = encode_tmap_bf16_3d(&tq, Q, (uint64_t)B * H, S, D, 128, 64)) != PTXB200_OK) return rc;
-  if ((rc = encode_tmap_bf16_3d(&tk, K, (uint64_t)B * H_kv, S, D, 128, 64)) != PTXB200_OK) return rc;
-  if ((rc = encode_tmap_bf16_3d(&tv, V, (uint64_t)B * H_kv, S, D, 128, 64)) != PTXB200_OK) return rc;
-  FaParams p;
+// The parameters every entry point fills the same way. `sc` is the distribution
+// plan_schedule chose: without a cut last round only its pair_mode is used.
+void fill_params(FaParams& p, void* O, void* lse, int B, int H, int H_kv, int S, float sm_scale, unsigned flags,
+                 void* dbg, uint32_t* status, const FaSched& sc) {
   p.o = reinterpret_cast<__nv_bfloat16*>(O);
   p.seqlen = S;
   p.num_mblocks = (S + 255) / 256;
@@ -852,14 +1257,83 @@ int launch_fa_fwd(const DeviceCtx& ctx, void* O, void* lse, const void* Q, const
   p.lse = reinterpret_cast<float*>(lse);
   p.heads_q = H;
   p.heads_kv = H_kv;
-  p.pair_mode = (causal && !(flags & PTXB200_FA_SINGLE_BLOCKS))
-                    ? causal_pair_mode(p.bh, p.num_mblocks, (S + kAttnRows - 1) / kAttnRows, ctx.sm_count) : 0;
-  if (D == 128) {
-    return causal ? launch_variant<128, true>(ctx, tq, tk, tv, p, stream)
-                  : launch_variant<128, false>(ctx, tq, tk, tv, p, stream);
+  p.pair_mode = sc.pair_mode;
+  p.sched = sc;
+  p.parts = nullptr;
+  p.part_flags = nullptr;
+  p.epoch = 0;
+}
+
+}  // namespace
+
+int launch_fa_fwd(const DeviceCtx& ctx, void* O, void* lse, const void* Q, const void* K,
+                  const void* V, int B, int H, int H_kv, int S, int D, float sm_scale, int causal,
+                  unsigned flags, void* dbg, uint32_t* status, cudaStream_t stream) {
+  CUtensorMap tq, tk, tv;
+  int rc;
+  if ((rc = encode_tmap_bf16_3d(&tq, Q, (uint64_t)B * H, S, D, 128, 64)) != PTXB200_OK) return rc;
+  if ((rc = encode_tmap_bf16_3d(&tk, K, (uint64_t)B * H_kv, S, D, 128, 64)) != PTXB200_OK) return rc;
+  if ((rc = encode_tmap_bf16_3d(&tv, V, (uint64_t)B * H_kv, S, D, 128, 64)) != PTXB200_OK) return rc;
+  FaParams p;
+  fill_params(p, O, lse, B, H, H_kv, S, sm_scale, flags, dbg, status,
+              plan_schedule(B * H, (S + 255) / 256, (S + kAttnRows - 1) / kAttnRows, causal, flags, ctx.sm_count, true));
+  ScratchLease lease;
+  if (p.sched.tail_units > 0) {
+    // one slot of parked pieces and one flag per CTA, kept per (device, stream)
+    const size_t slot = D == 128 ? parts_slot_bytes<128>() : parts_slot_bytes<64>();
+    if ((rc = scratch_acquire(ctx, stream, kScratchAttnParts, kPartsHeaderBytes + (size_t)ctx.sm_count * slot,
+                              &lease)) != PTXB200_OK)
+      return rc;
+    if (lease.fresh) PTXB200_CUDA_TRY(cudaMemsetAsync(lease.ptr, 0, kPartsHeaderBytes, stream));
+    p.part_flags = reinterpret_cast<uint32_t*>(lease.ptr);
+    p.parts = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(lease.ptr) + kPartsHeaderBytes);
+    p.epoch = lease.epoch;
   }
-  return causal ? launch_variant<64, true>(ctx, tq, tk, tv, p, stream)
+  if (D == 128) {
+    rc = causal ? launch_variant<128, true>(ctx, tq, tk, tv, p, stream)
+                : launch_variant<128, false>(ctx, tq, tk, tv, p, stream);
+  } else {
+    rc = causal ? launch_variant<64, true>(ctx, tq, tk, tv, p, stream)
                 : launch_variant<64, false>(ctx, tq, tk, tv, p, stream);
+  }
+  if (rc != PTXB200_OK) return rc;
+  if (p.sched.tail_units > 0) return scratch_mark_used(lease, stream);
+  return PTXB200_OK;
+}
+
+// The distribution plan_schedule picks and every tail CTA's segments, for tests on a
+// machine without a GPU. out: 10 ints of FaSched (num_mblocks, bh, nt_all, causal, pair_mode,
+// grid, full_units, tail_units, tail_steps, tail_ctas), then per tail CTA its segment count
+// followed by 6 ints per segment (mb, bh, j0, j1, len, n_other). Returns the ints written,
+// or -1 if `cap` is too small.
+int describe_fa_plan(int BH, int S, int causal, unsigned flags, int sm_count, int* out, int cap) {
+  const int nmb = (S + 255) / 256, nt_all = (S + kAttnRows - 1) / kAttnRows;
+  const FaSched sc = plan_schedule(BH, nmb, nt_all, causal, flags, sm_count, true);
+  int n = 0;
+  auto put = [&](int v) {
+    if (n < cap) out[n] = v;
+    ++n;
+  };
+  put(sc.num_mblocks); put(sc.bh); put(sc.nt_all); put(sc.causal); put(sc.pair_mode);
+  put(sc.grid); put(sc.full_units); put(sc.tail_units); put(sc.tail_steps); put(sc.tail_ctas);
+  if (sc.tail_units > 0) {
+    std::vector<int> starts(sc.tail_units + 1, 0);
+    for (int u = 0; u < sc.tail_units; ++u) {
+      int la, lb;
+      fa_unit_lens(sc, sc.full_units + u, la, lb);
+      starts[u + 1] = starts[u] + la + lb;
+    }
+    HostLocator loc{starts.data(), (int)starts.size() - 1};
+    for (int c = 0; c < sc.tail_ctas; ++c) {
+      FaSeg segs[kTailMaxSegs];
+      const int k = fa_tail_segments(sc, c, loc, segs);
+      put(k);
+      for (int i = 0; i < k && i < kTailMaxSegs; ++i) {
+        put(segs[i].mb); put(segs[i].bh); put(segs[i].j0); put(segs[i].j1); put(segs[i].len); put(segs[i].n_other);
+      }
+    }
+  }
+  return n <= cap ? n : -1;
 }
 
 }  // namespace ptxb200
@@ -933,7 +1407,8 @@ extern "C" int fa_fwd_bf16_noalloc(void* O, const void* Q, const void* K, const 
   if (O == nullptr || Q == nullptr || K == nullptr || V == nullptr) return PTXB200_E_INVALID;
   if (B <= 0 || H <= 0 || S <= 0 || D <= 0) return PTXB200_E_INVALID;
   if (causal != 0 && causal != 1) return PTXB200_E_INVALID;
-  if (flags & ~(PTXB200_FA_NO_LAZY_RESCALE | PTXB200_FA_SINGLE_BLOCKS)) return PTXB200_E_INVALID;
+  if (flags & ~(PTXB200_FA_NO_LAZY_RESCALE | PTXB200_FA_SINGLE_BLOCKS | PTXB200_FA_NO_TAIL_SPLIT |
+                PTXB200_FA_ALWAYS_TAIL_SPLIT)) return PTXB200_E_INVALID;
   if (!(sm_scale > 0.0f) || !(sm_scale < 1e30f)) return PTXB200_E_INVALID;
   if ((D != 64 && D != 128) || (S % 128 != 0 && !causal)) return PTXB200_E_SHAPE;
   if ((long long)B * H * S >= (1ll << 31)) return PTXB200_E_SHAPE;
@@ -975,21 +1450,11 @@ extern "C" int fa_fwd_bf16_noalloc(void* O, const void* Q, const void* K, const 
   }
 
   FaParams p;
-  p.o = reinterpret_cast<__nv_bfloat16*>(O);
-  p.seqlen = S;
-  p.num_mblocks = (S + 255) / 256;
-  p.bh = B * H;
-  p.total_work = p.num_mblocks * p.bh;
-  p.scale_log2 = sm_scale * 1.4426950408889634f;
-  p.rescale_threshold = (flags & PTXB200_FA_NO_LAZY_RESCALE) ? 0.0f : 8.0f;
-  p.status = nd.scratch;
-  p.dbg = nullptr;
+  // whole items only: cutting the last round along the key axis needs scratch in proportion
+  // to the SM count, which this entry point does not have
+  fill_params(p, O, nullptr, B, H, H, S, sm_scale, flags, nullptr, nd.scratch,
+              plan_schedule(B * H, (S + 255) / 256, (S + kAttnRows - 1) / kAttnRows, causal, flags, nd.sm_count, false));
   p.cta_flags = nd.scratch + kNoAllocFlagBase;
-  p.lse = nullptr;
-  p.heads_q = H;
-  p.heads_kv = H;
-  p.pair_mode = (causal && !(flags & PTXB200_FA_SINGLE_BLOCKS))
-                    ? causal_pair_mode(p.bh, p.num_mblocks, (S + kAttnRows - 1) / kAttnRows, nd.sm_count) : 0;
   const int units = (causal && p.pair_mode) ? p.bh * ((p.num_mblocks + 1) / 2) : p.total_work;
   const int grid = units < nd.sm_count ? units : nd.sm_count;
   if (grid > kNoAllocMaxCtas) {

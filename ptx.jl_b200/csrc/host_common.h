@@ -77,6 +77,8 @@ constexpr int kScratchMaxEntries = 16;
 struct ScratchLease {
   void* ptr = nullptr;
   int entry = -1;
+  bool fresh = false;      // allocated by this call: contents undefined
+  uint32_t epoch = 0;      // counts the leases of this buffer, from 1; never 0
 };
 int scratch_acquire(const DeviceCtx& ctx, cudaStream_t stream, int kind, size_t bytes, ScratchLease* out);
 int scratch_mark_used(const ScratchLease& lease, cudaStream_t stream);
@@ -121,6 +123,8 @@ int launch_gemm(const DeviceCtx& ctx, void* C, const void* A, const void* Bt, in
 int launch_fa_fwd(const DeviceCtx& ctx, void* O, void* lse, const void* Q, const void* K,
                   const void* V, int B, int H, int H_kv, int S, int D, float sm_scale, int causal,
                   unsigned flags, void* dbg, uint32_t* status, cudaStream_t stream);
+// The work distribution launch_fa_fwd would pick, as plain ints (fa_fwd_sm100.cu).
+int describe_fa_plan(int BH, int S, int causal, unsigned flags, int sm_count, int* out, int cap);
 // CTA-pair GEMM (gemm2_sm100.cu): whether it applies to a shape, and its launcher.
 bool gemm_pair_eligible(const DeviceCtx& ctx, int groups, int M, int N, int K);
 int launch_gemm_pair(const DeviceCtx& ctx, void* C, const void* A, const void* Bt, int groups, int M, int N,

@@ -177,6 +177,38 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
 }
 
 // ---------------------------------------------------------------------------
+// Flags in global memory between CTAs of one launch (release / acquire at GPU scope).
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void st_release_gpu(uint32_t* p, uint32_t v) {
+  asm volatile("st.global.release.gpu.b32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.global.acquire.gpu.b32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// Bounded wait until *flag == want (written by another CTA of the same launch with
+// st_release_gpu). Same expiry behaviour as mbar_wait: first blame, CTA abort flag,
+// return false.
+__device__ __forceinline__ bool flag_wait(const uint32_t* flag, uint32_t want, const WaitCtx& ctx,
+                                          uint32_t site) {
+  if (ld_acquire_gpu(flag) == want) return true;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (true) {
+    if (ld_acquire_gpu(flag) == want) return true;
+    if (*ctx.abort != 0) return false;
+    if ((++spins & 15u) == 0 && globaltimer_ns() - t0 > kWaitLimitNs) {
+      *ctx.abort = 1;
+      if (ctx.status != nullptr)
+        atomicCAS(ctx.status, 0u, kStatusTimeoutTag | (site << 8) | ((blockIdx.x & 0x7Fu) << 1));
+      return false;
+    }
+    __nanosleep(64);
+  }
+}
+
+// ---------------------------------------------------------------------------
 // TMA (cp.async.bulk.tensor) 2-D tile load, completion counted in bytes on an
 // mbarrier. c0 is the innermost (contiguous) coordinate, in elements; c0 times
 // the element size must be a multiple of 16 bytes.

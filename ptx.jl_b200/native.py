@@ -21,6 +21,8 @@ GEMM_NO_SPLIT = 0x2
 GEMM_ONE_CTA = 0x4
 FA_NO_LAZY_RESCALE = 0x1
 FA_SINGLE_BLOCKS = 0x2
+FA_NO_TAIL_SPLIT = 0x4
+FA_ALWAYS_TAIL_SPLIT = 0x8
 
 E_INVALID, E_SHAPE, E_ALIGN, E_CUDA, E_DRIVER, E_DEVICE, E_CAPACITY = -1, -2, -3, -4, -5, -6, -7
 
@@ -82,6 +84,8 @@ def lib() -> ctypes.CDLL:
     L.fa_fwd_bf16_noalloc_status.argtypes = [vp, ci, vp]
     L.ptxb200_sync_status.restype = ci
     L.ptxb200_sync_status.argtypes = [vp]
+    L.ptxb200_fa_plan.restype = ci
+    L.ptxb200_fa_plan.argtypes = [ci, ci, ci, ci, cu, ci, vp, ci]
     L.ptxb200_device_status.restype = ci
     L.ptxb200_device_status.argtypes = []
     L.ptxb200_selftest.restype = ci

@@ -161,8 +161,10 @@ def test_causal_schedules_agree_bit_for_bit(pkg, gpu, B, H, S, D):
     q, k, v = (t.to(gpu) for t in seeded_qkv(B, H, S, D, 4242 + S, 0.7))
     lse_a = torch.empty(B * H * S, dtype=torch.float32, device=gpu)
     lse_b = torch.empty_like(lse_a)
-    a = pkg.ops.fa_fwd(q, k, v, causal=True, lse=lse_a)
-    b = pkg.ops.fa_fwd(q, k, v, causal=True, lse=lse_b, flags=pkg.native.FA_SINGLE_BLOCKS)
+    # (the last round is left uncut in both: a cut changes the key order of the rows it touches)
+    keep = pkg.native.FA_NO_TAIL_SPLIT
+    a = pkg.ops.fa_fwd(q, k, v, causal=True, lse=lse_a, flags=keep)
+    b = pkg.ops.fa_fwd(q, k, v, causal=True, lse=lse_b, flags=keep | pkg.native.FA_SINGLE_BLOCKS)
     assert pkg.ops.sync_status() == 0
     assert torch.equal(a, b) and torch.equal(lse_a, lse_b)
 
@@ -266,10 +268,16 @@ def test_seeded_random_shapes(pkg, gpu, oracle_mod, B, H, H_kv, S, D, causal, se
                                      bits(ve).reshape(B * H, S, D), 1.0 / D ** 0.5, causal)
     mx, mean = attn_errors(o, ref)
     assert mx <= ATTN_MAX_ABS and mean <= ATTN_MEAN_ABS, (mx, mean)
+    # with the last round left uncut the result is the same up to the re-association of the
+    # cut rows' sums, and the two causal schedules then agree bit for bit
+    keep = pkg.native.FA_NO_TAIL_SPLIT
+    o1 = pkg.ops.fa_fwd(qd, kd, vd, causal=causal, flags=keep)
+    assert pkg.ops.sync_status() == 0
+    assert (o.float() - o1.float()).abs().max().item() <= 2 ** -6
     if causal:
-        o2 = pkg.ops.fa_fwd(qd, kd, vd, causal=True, flags=pkg.native.FA_SINGLE_BLOCKS)
+        o2 = pkg.ops.fa_fwd(qd, kd, vd, causal=True, flags=keep | pkg.native.FA_SINGLE_BLOCKS)
         assert pkg.ops.sync_status() == 0
-        assert torch.equal(o, o2)
+        assert torch.equal(o1, o2)
 
 
 def test_rejects_bad_arguments(pkg, gpu):
@@ -284,3 +292,93 @@ def test_rejects_bad_arguments(pkg, gpu):
     assert L.fa_fwd_bf16(P, P + 2, P, P, 1, 1, 256, 128, sc, 0, 0, None, None) == pkg.native.E_ALIGN
     assert L.fa_fwd_bf16(P, P, P, P, 1, 1, 256, 128, sc, 2, 0, None, None) == pkg.native.E_INVALID
     assert L.fa_fwd_bf16(P, P, P, P, 1, 1, 256, 128, sc, 0, 0x80, None, None) == pkg.native.E_INVALID
+
+
+# ---------------------------------------------------------------------------
+# The last round cut along the key axis (no reference counterpart: the reference deals whole
+# items, test/gpu/blackwell/flash_attention_defs.jl:269-272). Shapes whose item count leaves
+# the last round partly filled on this GPU; each is checked against the oracle, against the
+# uncut launch, and for reproducibility from launch to launch.
+# ---------------------------------------------------------------------------
+def _plan_header(pkg, B, H, S, causal, flags=0):
+    import ctypes
+    sm = torch.cuda.get_device_properties(0).multi_processor_count
+    cap = 16 + sm * 49
+    buf = (ctypes.c_int * cap)()
+    n = pkg.native.lib().ptxb200_fa_plan(B, H, S, int(causal), flags, sm, buf, cap)
+    assert n >= 10
+    return dict(zip(["nmb", "bh", "nt_all", "causal", "pair", "grid", "full", "tail_units", "tail_steps",
+                     "tail_ctas"], list(buf)[:10]))
+
+
+@pytest.mark.parametrize("B,H,H_kv,S,D,causal", [
+    (1, 8, 8, 4096, 128, False),    # an eighth of the headline problem: 128 items for 148 SMs
+    (2, 16, 16, 2048, 64, False),   # an eighth of the short-sequence configuration (D = 64)
+    (1, 4, 4, 8192, 128, True),     # causal pairs of 66 steps, fewer than SMs
+    (1, 5, 5, 8192, 64, True),
+    (3, 4, 2, 1000, 128, False),    # ragged length, grouped heads
+    (1, 7, 7, 1000, 64, True),
+    (1, 1, 1, 4096, 128, False),    # one head: every item in many pieces
+    (1, 2, 1, 2304, 128, True),     # odd block count: a middle block without partner
+    (5, 8, 8, 1536, 128, False),    # a full round, then a cut one
+    (3, 30, 30, 1280, 64, True),    # five blocks per head, a full round first
+    (2, 45, 45, 1024, 64, True),    # fewer CTAs share the cut round than run the launch
+])
+def test_cut_last_round_matches_oracle_and_uncut_launch(pkg, gpu, oracle_mod, B, H, H_kv, S, D, causal):
+    cut = pkg.native.FA_ALWAYS_TAIL_SPLIT     # (the default policy cuts only where it expects a clear gain)
+    assert _plan_header(pkg, B, H, S, causal, cut)["tail_units"] > 0, "this shape is meant to exercise the cut"
+    g = torch.Generator().manual_seed(B * 1000 + H * 10 + S)
+    q = torch.randn(B, H, S, D, generator=g).to(torch.bfloat16)
+    k = torch.randn(B, H_kv, S, D, generator=g).to(torch.bfloat16)
+    v = torch.randn(B, H_kv, S, D, generator=g).to(torch.bfloat16)
+    qd, kd, vd = q.to(gpu), k.to(gpu), v.to(gpu)
+    lse = torch.full((B, H, S), float("nan"), dtype=torch.float32, device=gpu)
+    lse_u = torch.empty_like(lse)
+    o = torch.full((B, H, S, D), float("nan"), dtype=torch.bfloat16, device=gpu)
+    pkg.ops.fa_fwd(qd, kd, vd, causal=causal, lse=lse, out=o, flags=cut)
+    o_again = pkg.ops.fa_fwd(qd, kd, vd, causal=causal, flags=cut)        # same scratch, next epoch
+    o_uncut = pkg.ops.fa_fwd(qd, kd, vd, causal=causal, lse=lse_u, flags=pkg.native.FA_NO_TAIL_SPLIT)
+    status = pkg.ops.sync_status()
+    assert status == 0, pkg.native.strerror(status)
+    assert not torch.isnan(o.float()).any() and not torch.isnan(lse).any()
+    assert torch.equal(o, o_again)
+    # the merge re-associates fp32 sums before the one rounding to bf16: at most a bf16 ulp apart
+    assert (o.float() - o_uncut.float()).abs().max().item() <= 2 ** -6
+    torch.testing.assert_close(lse, lse_u, rtol=0, atol=2e-5 * max(1.0, float(lse_u.abs().max())))
+    if B * H * S * S <= 5e8:
+        ke = k.repeat_interleave(H // H_kv, dim=1)
+        ve = v.repeat_interleave(H // H_kv, dim=1)
+        ref = oracle_mod.attention_ref_c(bits(q).reshape(B * H, S, D), bits(ke).reshape(B * H, S, D),
+                                         bits(ve).reshape(B * H, S, D), 1.0 / D ** 0.5, causal)
+        mx, mean = attn_errors(o, ref)
+        assert mx <= ATTN_MAX_ABS and mean <= ATTN_MEAN_ABS, (mx, mean)
+    else:
+        # too large for the oracle in test time: a few heads of it
+        for bh in (0, B * H - 1):
+            b_, h_ = divmod(bh, H)
+            hk = h_ // (H // H_kv)
+            ref = oracle_mod.attention_ref_c(bits(q[b_, h_])[None], bits(k[b_, hk])[None], bits(v[b_, hk])[None],
+                                             1.0 / D ** 0.5, causal)
+            mx, mean = attn_errors(o[b_, h_], ref)
+            assert mx <= ATTN_MAX_ABS and mean <= ATTN_MEAN_ABS, (bh, mx, mean)
+
+
+def test_cut_last_round_on_two_streams(pkg, gpu):
+    """Scratch for the parked pieces is per stream: launches that overlap on two streams
+    stay correct and reproducible."""
+    B, H, S, D = 1, 8, 2048, 128
+    cut = pkg.native.FA_ALWAYS_TAIL_SPLIT
+    assert _plan_header(pkg, B, H, S, False, cut)["tail_units"] > 0
+    sets = [[t.to(gpu) for t in seeded_qkv(B, H, S, D, 70 + i, 1.0)] for i in range(2)]
+    want = [pkg.ops.fa_fwd(*s, flags=cut) for s in sets]
+    torch.cuda.synchronize()
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    outs = [torch.empty_like(w) for w in want]
+    for _ in range(20):
+        for st, s, o in zip(streams, sets, outs):
+            pkg.ops.fa_fwd(*s, out=o, stream=st, flags=cut)
+    torch.cuda.synchronize()
+    assert pkg.ops.sync_status() == 0
+    for o, w in zip(outs, want):
+        assert torch.equal(o, w)
+

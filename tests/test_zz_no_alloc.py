@@ -47,7 +47,8 @@ def _status(pkg, n_flags=240):
 def test_noalloc_matches_regular_entry_point_twice(pkg, gpu, D, causal):
     B, H, S = 2, 40, 768           # more work items than SMs: every CTA loops over several
     q, k, v = (t.to(gpu) for t in seeded_qkv(B, H, S, D, 31 + D, 1.0))
-    want = pkg.ops.fa_fwd(q, k, v, causal=causal)
+    # (the sibling call with its last round left uncut, as this entry point always leaves it)
+    want = pkg.ops.fa_fwd(q, k, v, causal=causal, flags=pkg.native.FA_NO_TAIL_SPLIT)
     assert pkg.ops.sync_status() == 0
     for attempt in range(2):       # two calls in a row share the static scratch
         got = torch.full_like(want, float("nan"))
@@ -63,7 +64,7 @@ def test_noalloc_matches_regular_entry_point_twice(pkg, gpu, D, causal):
         assert not any(cta_flags)
     # different inputs right after: nothing stale is picked up from the scratch
     q2, k2, v2 = (t.to(gpu) for t in seeded_qkv(B, H, S, D, 977, 2.0))
-    want2 = pkg.ops.fa_fwd(q2, k2, v2, causal=causal)
+    want2 = pkg.ops.fa_fwd(q2, k2, v2, causal=causal, flags=pkg.native.FA_NO_TAIL_SPLIT)
     got2 = torch.empty_like(want2)
     assert _call_noalloc(pkg, got2, q2, k2, v2, causal) == 0
     torch.cuda.synchronize()
@@ -123,8 +124,10 @@ _FRESH = textwrap.dedent("""
         rc = L.fa_fwd_bf16_noalloc(outs[i].data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), B, H, S, D,
                                    ctypes.c_float(1.0 / D ** 0.5), causal, 0, None)
         assert rc == 0, rc
-    # first use of each kernel variant loads its code; nothing else of this library has run
+    # first use of each kernel variant loads its code (and torch's fill kernel, used below,
+    # loads with its own first call); nothing else of this library has run
     for i in range(len(cases)):
+        outs[i].fill_(float("nan"))
         call(i)
     assert L.fa_fwd_bf16_noalloc_status(None, 0, None) == 0
     torch.cuda.synchronize()
