@@ -419,8 +419,9 @@ def quantisation_note(pkg, name, world, sm):
     B, H, S, D, causal, _, _ = WORKLOADS[name]
     items = (B * H // world) * ((S + 255) // 256)
     waves = items / sm
-    return (f"{items} items of 256 rows on {sm} SMs = {waves:.2f} rounds: whole items alone allow "
-            f"{waves / math.ceil(waves):.2f} of linear; the last round is cut along the key axis")
+    return (f"{items} items of 256 rows on {sm} SMs = {waves:.2f} rounds: whole items allow "
+            f"{waves / math.ceil(waves):.2f} of linear (the last round is cut along the key axis only where that "
+            f"is expected to pay)")
 
 
 def run_native_arm(args):
@@ -493,6 +494,32 @@ def run_native_arm(args):
     else:
         peak, peak_text = peak_hbm, f"{peak_kind} (copy)"
 
+    # ---- the other configurations, one burst each, and the fixed problems split over the ranks ----
+    configs, strong, problems = {}, {}, {}
+    extra = args.workload == "c2" and not args.headline_only
+    head_mhz = head["clocks"]["sm_mhz"]
+    if extra:
+        # one burst of each other configuration, right behind the headline (same, cool state)
+        problems["c2"] = prob
+        for name in ("c3", "c4", "c5"):
+            is_gemm = name in GEMM_WORKLOADS
+            steps_n = {"c4": 5}.get(name, 20)
+            full = gemm_problem(ops, dev, name, 0) if is_gemm else attention_problem(ops, dev, name)
+            problems[name] = full
+            full_t = bench.measure(lambda: full.run(full.inputs, full.out), steps_n, 3, repeats=3)
+            check_status(f"configs.{name}")
+            tf = full.work / (full_t["ms"] * 1e-3) / 1e12
+            configs[name] = {"workload": full.text, "ms": full_t["ms"], "ms_min": full_t["ms_min"],
+                             "ms_max": full_t["ms_max"], "tflops": tf, "frac_of_burst_peak": tf / peak_burst,
+                             "frac_of_sustained_peak": tf / peak_sustained,
+                             "steps": steps_n, "repeats": 3, "sm_mhz": full_t["clocks"]["sm_mhz"],
+                             "kcycles_per_launch": (full_t["ms"] * full_t["clocks"]["sm_mhz"]
+                                                    if full_t["clocks"]["sm_mhz"] else None)}
+            if name == "c3":
+                # at D = 64 the exponentials, not the tensor pipe, bound a tile: 16 ex2/clk/SM on the
+                # MUFU (measured: profiles/ex2_throughput.md) against 2*D flop per score on the tensor pipe
+                configs[name]["mufu_ceiling_tflops"] = 4.0 * 64 * 16 * sm_count * (full_t["clocks"]["sm_mhz"] or 0) * 1e6 / 1e12
+
     # ---- sustained: one region of at least half a second (power management settles) ----
     sustained = None
     if bound == "tensor":
@@ -506,65 +533,76 @@ def run_native_arm(args):
                      "frac": tf_long / peak_sustained, "peak_kind": f"{peak_kind} (sustained cuBLAS bf16)",
                      "clocks": clk_long,
                      "kcycles_per_launch": (ms_long / n_long) * mhz if mhz else None}
-    head_mhz = head["clocks"]["sm_mhz"]
 
-    # ---- the other configurations, one burst each, and the fixed problems split over the ranks ----
-    configs, strong = {}, {}
-    if args.workload == "c2" and not args.headline_only:
+    if extra:
+        # the fixed problems split over the ranks ("strong"), after the long region: steady clocks
         for name in ("c2", "c3", "c4", "c5"):
             is_gemm = name in GEMM_WORKLOADS
             steps_n = {"c4": 5}.get(name, 20)
-            if name == "c2":
-                full, full_t = prob, head
-            else:
-                full = gemm_problem(ops, dev, name, 0) if is_gemm else attention_problem(ops, dev, name)
-                full_t = bench.measure(lambda: full.run(full.inputs, full.out), steps_n, 3, repeats=3)
-                check_status(f"configs.{name}")
-                tf = full.work / (full_t["ms"] * 1e-3) / 1e12
-                configs[name] = {"workload": full.text, "ms": full_t["ms"], "ms_min": full_t["ms_min"],
-                                 "ms_max": full_t["ms_max"], "tflops": tf, "frac_of_burst_peak": tf / peak_burst,
-                                 "steps": steps_n, "repeats": 3, "sm_mhz": full_t["clocks"]["sm_mhz"],
-                                 "kcycles_per_launch": (full_t["ms"] * full_t["clocks"]["sm_mhz"]
-                                                        if full_t["clocks"]["sm_mhz"] else None)}
-                if name == "c3":
-                    # at D = 64 the exponentials, not the tensor pipe, bound a tile: 16 ex2/clk/SM on the
-                    # MUFU (measured: profiles/ex2_throughput.md) against 2*D flop per score on the tensor pipe
-                    configs[name]["mufu_ceiling_tflops"] = 4.0 * 64 * 16 * sm_count * (full_t["clocks"]["sm_mhz"] or 0) * 1e6 / 1e12
+            full = problems[name]
 
             def shard_launcher(n_ranks, r):
+                # a shard writes to a buffer of its own: the resident output of the headline run stays
+                # what the end-to-end leg is compared with
                 if is_gemm:
                     a, bt = full.inputs
                     b, e = pkg.sharding.gemm_column_shard(bt.shape[0], r, n_ranks)
                     bt_s = bt[b:e]
                     out = torch.empty(a.shape[0], e - b, device=dev, dtype=torch.bfloat16)
-                    return (lambda: full.run([a, bt_s], out)), full.work * (e - b) / bt.shape[0], f"{e - b} of {bt.shape[0]} columns"
-                ins, out, work, n_sl = attention_shard(pkg, full, r, n_ranks)
-                return (lambda: full.run(ins, out)), work, f"{n_sl} of {full.inputs[0].shape[0] * full.inputs[0].shape[1]} (batch, head) slices"
+                    return (lambda: full.run([a, bt_s], out)), f"{e - b} of {bt.shape[0]} columns"
+                ins, out_view, _, n_sl = attention_shard(pkg, full, r, n_ranks)
+                out = torch.empty_like(out_view)
+                return (lambda: full.run(ins, out)), f"{n_sl} of {full.inputs[0].shape[0] * full.inputs[0].shape[1]} (batch, head) slices"
 
-            entry = {"t1_ms": full_t["ms"], "workload": full.text}
+            def timed(launch):
+                # regions of at least 25 ms each, so that both sides of a ratio sit in the same power
+                # state and the clock sampler sees each region
+                probe = bench.measure(launch, 5, 3, repeats=1)["ms"]
+                n = int(bench.max_over_ranks(max(steps_n, math.ceil(25.0 / max(probe, 1e-3)))))
+                t = bench.measure(launch, n, 3, repeats=3)
+                mhz = t["clocks"]["sm_mhz"]
+                return t["ms"], (t["ms"] * mhz if mhz else None)
+
+            # the whole problem is timed again right before and right after its shards, so that
+            # both sides of the ratio see the same clocks (the headline above ran on a cooler GPU)
+            full_launch = lambda: full.run(full.inputs, full.out)
+            f0_ms, f0_kc = timed(full_launch)
+            entry = {"workload": full.text}
             if world > 1:
-                launch, work, what = shard_launcher(world, rank)
-                t = bench.measure(launch, steps_n, 3, repeats=3)
-                check_status(f"strong.{name}")
-                entry.update({"n": world, "shard_per_rank": what, "ms": t["ms"],
-                              "tflops_total": full.work / (t["ms"] * 1e-3) / 1e12,
-                              "efficiency": full_t["ms"] / (world * t["ms"]),
-                              "bound": quantisation_note(pkg, name, world, sm_count)})
+                launch, what = shard_launcher(world, rank)
+                sh_ms, sh_kc = timed(launch)
+                shards = {str(world): (what, sh_ms, sh_kc)}
             else:
                 # one GPU: the shards a rank would hold at 2, 4 and 8 ranks, timed one after the
                 # other (ranks are independent: no collective on the path)
-                emu = {}
+                shards = {}
                 for n_ranks in (2, 4, 8):
-                    launch, work, what = shard_launcher(n_ranks, 0)
-                    t = bench.measure(launch, steps_n, 3, repeats=3)
-                    emu[str(n_ranks)] = {"shard": what, "ms": t["ms"], "efficiency": full_t["ms"] / (n_ranks * t["ms"])}
-                check_status(f"strong.{name} (emulated)")
-                entry.update({"n": 1, "efficiency": 1.0, "single_gpu_emulation": emu,
-                              "bound_at_8": quantisation_note(pkg, name, 8, sm_count)})
+                    launch, what = shard_launcher(n_ranks, 0)
+                    sh_ms, sh_kc = timed(launch)
+                    shards[str(n_ranks)] = (what, sh_ms, sh_kc)
+            f1_ms, f1_kc = timed(full_launch)
+            check_status(f"strong.{name}")
+            t1_ms = 0.5 * (f0_ms + f1_ms)
+            t1_kc = 0.5 * (f0_kc + f1_kc) if (f0_kc and f1_kc) else None
+            entry["t1_ms"] = t1_ms
+            entry["t1_kcycles"] = t1_kc
+
+            def eff(n_ranks, sh_ms, sh_kc):
+                return {"ms": sh_ms, "tflops_total": full.work / (sh_ms * 1e-3) / 1e12,
+                        "efficiency": t1_ms / (n_ranks * sh_ms),
+                        "efficiency_in_cycles": (t1_kc / (n_ranks * sh_kc)) if (t1_kc and sh_kc) else None,
+                        "bound": quantisation_note(pkg, name, n_ranks, sm_count)}
+
+            if world > 1:
+                what, sh_ms, sh_kc = shards[str(world)]
+                entry.update({"n": world, "shard_per_rank": what, **eff(world, sh_ms, sh_kc)})
+            else:
+                entry.update({"n": 1, "efficiency": 1.0,
+                              "single_gpu_emulation": {k: {"shard": v[0], **eff(int(k), v[1], v[2])}
+                                                       for k, v in shards.items()}})
             strong[name] = entry
-            if name != "c2":
-                del full
-                torch.cuda.empty_cache()
+        problems.clear()
+        torch.cuda.empty_cache()
 
     # ---- end to end: host buffers in, host buffer out, copies inside the timed region ----
     inputs, o = prob.inputs, prob.out

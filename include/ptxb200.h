@@ -310,8 +310,14 @@ int ptxb200_device_status(void);
  *      (1.5 s), and the kernel returns. out: 3 uint32 = {0, 0, 0xD0E5} (both waits
  *      report failure, the kernel reached its end); the next ptxb200_sync_status
  *      returns the positive code of wait site 15 ("probe").
+ *   4  throughput of one SM's exponential unit (no reference counterpart; the
+ *      reference's kernel comments assume 16 ex2 per clock per SM,
+ *      flash_attention_defs.jl:355-387): one CTA of 16 warps runs five timed passes --
+ *      4, 8 and 16 warps of nothing but ex2.approx, then 8 and 16 warps of the softmax's
+ *      inner mix (packed fma, two ex2, packed add, bf16 pack). out: 16 uint32;
+ *      out[2k] = cycles of pass k, out[2k+1] = ex2 executed in it.
  * For 1 and 2: q,k,v are (128, D) bf16, p is (128,128) bf16, all row-major.
- * Unused pointers may be NULL for probes 0 and 3.
+ * Unused pointers may be NULL for probes 0, 3 and 4.
  */
 int ptxb200_selftest(int which, void* out_s, void* out_o, const void* q, const void* k,
                      const void* v, const void* p, void* stream);

@@ -432,9 +432,9 @@ int ptxb200_device_status(void) {
 
 int ptxb200_selftest(int which, void* out_s, void* out_o, const void* q, const void* k,
                      const void* v, const void* p, void* stream) {
-  if (which < 0 || which > 3) return PTXB200_E_INVALID;
+  if (which < 0 || which > 4) return PTXB200_E_INVALID;
   if (out_s == nullptr) return PTXB200_E_INVALID;
-  if (which != 0 && which != 3 && (out_o == nullptr || q == nullptr || k == nullptr || v == nullptr || p == nullptr))
+  if (which != 0 && which != 3 && which != 4 && (out_o == nullptr || q == nullptr || k == nullptr || v == nullptr || p == nullptr))
     return PTXB200_E_INVALID;
   if (!aligned16(out_s) || !aligned16(out_o) || !aligned16(q) || !aligned16(k) || !aligned16(v) ||
       !aligned16(p))

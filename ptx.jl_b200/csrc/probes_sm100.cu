@@ -192,6 +192,69 @@ __global__ void __launch_bounds__(32, 1) wait_expiry_kernel(uint32_t* out, uint3
   if (threadIdx.x == 0) out[2] = 0xD0E5u;   // the kernel ran to its end
 }
 
+// Throughput of the exponential unit of one SM, the second bound of the attention kernel
+// (its softmax needs one ex2 per score: as many MUFU cycles per 128 x 128 tile as the tensor
+// pipe needs at head dim 128, twice as many at head dim 64). One CTA of 16 warps; five
+// passes, each timed with clock64 from the barrier before it to the barrier after it:
+//   pass 0-2: 4, 8, 16 warps issue nothing but independent ex2.approx.ftz (8 chains each)
+//   pass 3-4: 8, 16 warps run the softmax's inner mix per pair of scores -- one packed
+//             fma (scale and basis), two ex2, one packed add (row sum), one bf16x2 pack
+// out[2 * pass] = cycles, out[2 * pass + 1] = ex2 executed by the pass (all warps).
+constexpr int kEx2Iters = 2048;
+__global__ void __launch_bounds__(512, 1) ex2_throughput_kernel(uint32_t* out, float seed) {
+  const int warp = threadIdx.x >> 5;
+  __shared__ long long t_start;
+  float sink = 0.0f;
+  for (int pass = 0; pass < 5; ++pass) {
+    const int warps = pass == 0 ? 4 : (pass == 1 || pass == 3) ? 8 : 16;
+    __syncthreads();
+    if (threadIdx.x == 0) asm volatile("mov.u64 %0, %%clock64;" : "=l"(t_start));
+    __syncthreads();
+    if (warp < warps) {
+      if (pass < 3) {
+        float a[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) a[i] = seed - 0.01f * (float)(i + (threadIdx.x & 31));
+#pragma unroll 1
+        for (int r = 0; r < kEx2Iters; ++r) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) a[i] = ex2_approx(a[i]) - 1.5f;   // stays in (-1.5, 0): never saturates
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) sink += a[i];
+      } else {
+        float2 x[4], sum = make_float2(0.0f, 0.0f);
+        uint32_t acc = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) x[i] = make_float2(seed - 0.1f * i, seed - 0.05f * i - 0.01f * (threadIdx.x & 31));
+        const float2 sc = make_float2(0.999f, 0.999f), ng = make_float2(-0.01f, -0.01f);
+#pragma unroll 1
+        for (int r = 0; r < kEx2Iters; ++r) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 y = __ffma2_rn(x[i], sc, ng);
+            float2 e;
+            e.x = ex2_approx(y.x);
+            e.y = ex2_approx(y.y);
+            sum = __fadd2_rn(sum, e);
+            acc ^= pack_bf16x2(e.x, e.y);
+            x[i] = make_float2(e.x - 1.5f, e.y - 1.5f);
+          }
+        }
+        sink += sum.x + sum.y + __uint_as_float(acc & 0x3F800000u);
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      long long t_end;
+      asm volatile("mov.u64 %0, %%clock64;" : "=l"(t_end));
+      out[2 * pass] = (uint32_t)(t_end - t_start);
+      out[2 * pass + 1] = (uint32_t)(warps * 32 * kEx2Iters * 8);
+    }
+  }
+  if (sink == 12345.678f) out[15] = 1;   // keeps the arithmetic alive
+}
+
 }  // namespace
 
 int launch_selftest(const DeviceCtx& ctx, int which, void* out_s, void* out_o, const void* q,
@@ -205,6 +268,10 @@ int launch_selftest(const DeviceCtx& ctx, int which, void* out_s, void* out_o, c
     case 2: return launch_tile_probe<64>(ctx, out_s, out_o, q, k, v, p, stream);
     case 3:
       wait_expiry_kernel<<<1, 32, 0, stream>>>(reinterpret_cast<uint32_t*>(out_s), status_word(ctx, stream));
+      PTXB200_CUDA_TRY(cudaGetLastError());
+      return PTXB200_OK;
+    case 4:
+      ex2_throughput_kernel<<<1, 512, 0, stream>>>(reinterpret_cast<uint32_t*>(out_s), -0.75f);
       PTXB200_CUDA_TRY(cudaGetLastError());
       return PTXB200_OK;
     default: return PTXB200_E_INVALID;

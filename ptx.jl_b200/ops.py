@@ -238,9 +238,9 @@ def selftest(which: int, q=None, k=None, v=None, p=None):
         rc = native.lib().ptxb200_selftest(0, _ptr(out_s), None, None, None, None, None, _stream(None))
         native.check(rc)
         return out_s.view(128, 128), None
-    if which == 3:
-        out_s = torch.zeros(4, dtype=torch.int32, device=dev)
-        rc = native.lib().ptxb200_selftest(3, _ptr(out_s), None, None, None, None, None, _stream(None))
+    if which == 3 or which == 4:
+        out_s = torch.zeros(16, dtype=torch.int32, device=dev)
+        rc = native.lib().ptxb200_selftest(which, _ptr(out_s), None, None, None, None, None, _stream(None))
         native.check(rc)
         return out_s, None
     D = 128 if which == 1 else 64

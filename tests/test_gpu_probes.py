@@ -63,3 +63,16 @@ def test_bounded_wait_expiry_is_reported_and_the_device_stays_usable(pkg, gpu):
     assert "probe" in pkg.native.strerror(status)
     assert pkg.ops.sync_status() == 0             # reading the status cleared it
     test_tmem_roundtrip(pkg, gpu)                 # the device is as usable as before
+
+
+def test_ex2_throughput_probe(pkg, gpu):
+    """The exponential unit's throughput, the second bound of the attention kernel: at most
+    16 ex2 per clock per SM however many warps issue them (a saturated pipe with 16 warps),
+    and the softmax's inner mix stays within a fifth of that."""
+    out, _ = pkg.ops.selftest(4)
+    assert pkg.ops.sync_status() == 0
+    v = out.cpu().tolist()
+    rate = [v[2 * k + 1] / v[2 * k] for k in range(5)]
+    assert all(r <= 16.6 for r in rate), rate
+    assert rate[2] >= 14.0, rate          # 16 warps of pure ex2 saturate the pipe
+    assert rate[4] >= 0.75 * rate[2], rate
