@@ -376,7 +376,10 @@ class Bench:
             self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
         return float(t[0])
 
-    def warm(self, launch, min_launches, min_ms=25.0):
+    warm_ms = 25.0
+
+    def warm(self, launch, min_launches, min_ms=None):
+        min_ms = self.warm_ms if min_ms is None else min_ms
         t0, n = time.perf_counter(), 0
         while n < max(min_launches, 3) or (time.perf_counter() - t0) * 1e3 < min_ms:
             launch()
@@ -459,6 +462,7 @@ def run_native_arm(args):
     sampler = ClockSampler(physical_gpu_index(local_rank))
     sampler.start()
     bench = Bench(torch, dist, world, dev, sampler)
+    bench.warm_ms = args.warm_ms
 
     def check_status(where):
         status = ops.sync_status()
@@ -522,7 +526,7 @@ def run_native_arm(args):
 
     # ---- sustained: one region of at least half a second (power management settles) ----
     sustained = None
-    if bound == "tensor":
+    if bound == "tensor" and not args.headline_only:
         n_long = max(args.steps, int(math.ceil(600.0 / ms_per_step)))
         ms_long, clk_long = bench.region(lambda: prob.run(prob.inputs, prob.out), n_long)
         check_status("the sustained region")
@@ -734,7 +738,10 @@ def main():
                     default="c2")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--headline-only", action="store_true",
-                    help="skip the `configs` and `strong` blocks (the other configurations and the fixed problems split over the ranks)")
+                    help="skip the `sustained`, `configs` and `strong` blocks (the long region, the other "
+                         "configurations and the fixed problems split over the ranks): for profiler captures")
+    ap.add_argument("--warm-ms", type=float, default=25.0,
+                    help="minimum wall time of every warm-up (0 under a profiler, where each launch is replayed)")
     ap.add_argument("--rows", type=int, default=0,
                     help="row-wise workloads only: rows per GPU instead of the default (for small profiler captures)")
     args = ap.parse_args()

@@ -312,9 +312,10 @@ int ptxb200_device_status(void);
  *      returns the positive code of wait site 15 ("probe").
  *   4  throughput of one SM's exponential unit (no reference counterpart; the
  *      reference's kernel comments assume 16 ex2 per clock per SM,
- *      flash_attention_defs.jl:355-387): one CTA of 16 warps runs five timed passes --
+ *      flash_attention_defs.jl:355-387): one CTA of 16 warps runs seven timed passes --
  *      4, 8 and 16 warps of nothing but ex2.approx, then 8 and 16 warps of the softmax's
- *      inner mix (packed fma, two ex2, packed add, bf16 pack). out: 16 uint32;
+ *      inner mix (packed fma, two ex2, packed add, bf16 pack), then 8 and 16 warps of the
+ *      packed ex2.approx.ftz.bf16x2 (two exponentials per instruction). out: 16 uint32;
  *      out[2k] = cycles of pass k, out[2k+1] = ex2 executed in it.
  * For 1 and 2: q,k,v are (128, D) bf16, p is (128,128) bf16, all row-major.
  * Unused pointers may be NULL for probes 0, 3 and 4.

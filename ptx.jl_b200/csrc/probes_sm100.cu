@@ -199,14 +199,15 @@ __global__ void __launch_bounds__(32, 1) wait_expiry_kernel(uint32_t* out, uint3
 //   pass 0-2: 4, 8, 16 warps issue nothing but independent ex2.approx.ftz (8 chains each)
 //   pass 3-4: 8, 16 warps run the softmax's inner mix per pair of scores -- one packed
 //             fma (scale and basis), two ex2, one packed add (row sum), one bf16x2 pack
+//   pass 5-6: 8, 16 warps issue ex2.approx.ftz.bf16x2 (two exponentials per instruction)
 // out[2 * pass] = cycles, out[2 * pass + 1] = ex2 executed by the pass (all warps).
 constexpr int kEx2Iters = 2048;
 __global__ void __launch_bounds__(512, 1) ex2_throughput_kernel(uint32_t* out, float seed) {
   const int warp = threadIdx.x >> 5;
   __shared__ long long t_start;
   float sink = 0.0f;
-  for (int pass = 0; pass < 5; ++pass) {
-    const int warps = pass == 0 ? 4 : (pass == 1 || pass == 3) ? 8 : 16;
+  for (int pass = 0; pass < 7; ++pass) {
+    const int warps = pass == 0 ? 4 : (pass == 1 || pass == 3 || pass == 5) ? 8 : 16;
     __syncthreads();
     if (threadIdx.x == 0) asm volatile("mov.u64 %0, %%clock64;" : "=l"(t_start));
     __syncthreads();
@@ -222,6 +223,22 @@ __global__ void __launch_bounds__(512, 1) ex2_throughput_kernel(uint32_t* out, f
         }
 #pragma unroll
         for (int i = 0; i < 8; ++i) sink += a[i];
+      } else if (pass >= 5) {
+        // packed bf16 form: one instruction, two exponentials
+        uint32_t a[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) a[i] = pack_bf16x2(seed - 0.01f * i, seed - 0.02f * (threadIdx.x & 31));
+#pragma unroll 1
+        for (int r = 0; r < kEx2Iters; ++r) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            uint32_t e;
+            asm volatile("ex2.approx.ftz.bf16x2 %0, %1;" : "=r"(e) : "r"(a[i]));
+            a[i] = e ^ 0x80008000u;   // negate both halves: stays in (-2, 0)
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) sink += __uint_as_float(a[i] & 0x3F800000u);
       } else {
         float2 x[4], sum = make_float2(0.0f, 0.0f);
         uint32_t acc = 0;
@@ -249,7 +266,7 @@ __global__ void __launch_bounds__(512, 1) ex2_throughput_kernel(uint32_t* out, f
       long long t_end;
       asm volatile("mov.u64 %0, %%clock64;" : "=l"(t_end));
       out[2 * pass] = (uint32_t)(t_end - t_start);
-      out[2 * pass + 1] = (uint32_t)(warps * 32 * kEx2Iters * 8);
+      out[2 * pass + 1] = (uint32_t)(warps * 32 * kEx2Iters * 8 * (pass >= 5 ? 2 : 1));
     }
   }
   if (sink == 12345.678f) out[15] = 1;   // keeps the arithmetic alive
