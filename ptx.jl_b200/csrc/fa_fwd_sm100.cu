@@ -18,7 +18,8 @@
 //     mask only the diagonal tile, and are handed out longest first within a head;
 //   * the exponentials of a tile are split between two warps and two pipes: the
 //     stage's softmax warp does key columns 0-95 on the MUFU, the correction warp
-//     of the same rows does columns 96-127 with a polynomial on the FMA pipe;
+//     of the same rows does columns 96-127 with a polynomial on the FMA pipe (0-79 and
+//     80-127 in the head-dim-64 kernel without masking code, where the MUFU binds);
 //   * a protocol of mbarrier phases in which no producer can run two phases ahead
 //     of its consumer: within an item each producer's next arrival is downstream of
 //     an MMA issue that waited for the consumer's previous arrival, so no padding
@@ -69,6 +70,16 @@ constexpr int kRegsCorrection = PTXB200_FA_REGS_CORRECTION;
 constexpr int kRegsOther = PTXB200_FA_REGS_OTHER;
 static_assert(256 * kRegsSoftmax + 128 * kRegsCorrection + 128 * kRegsOther <= 65536,
               "register re-split must fit the register file");
+// Head dim 64: the exponential unit is the binding pipe there (one ex2 per score, half the
+// tensor work per score), so the correction warps take 48 instead of 32 of a tile's 128 key
+// columns onto the FMA pipe and get the registers for it. (At head dim 128 the same
+// split measured 2.4 % slower non-causal and spilled in the causal kernel.)
+constexpr int kRegsSoftmax64 = 160, kRegsCorrection64 = 120;
+static_assert(256 * kRegsSoftmax64 + 128 * kRegsCorrection64 + 128 * kRegsOther <= 65536,
+              "register re-split must fit the register file");
+// (only in the kernel without masking code: the causal and the ragged-length kernels
+// measured a quarter to a third slower with it at head dim 64)
+template <int D, bool kMasks> constexpr int kHelperCols = (D == 64 && !kMasks) ? 48 : 32;   // key columns per tile on the correction warps
 
 // Which of the 16 element pairs of every 32-column chunk take the FMA-pipe
 // polynomial exp2 instead of the MUFU ex2 (bit i = pair i). The MUFU pipe
@@ -652,7 +663,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
     // softmax: warpgroup `stage` owns the 128 rows of that stage; one row
     // per thread, the whole 128-column tile of scores in registers.
     // =====================================================================
-    setmaxnreg_inc<kRegsSoftmax>();
+    setmaxnreg_inc<(kHelperCols<D, kCausal || kRagged> == 48 ? kRegsSoftmax64 : kRegsSoftmax)>();
     const int stage = warp >> 2;
     const int row = tid & 127;
     const uint32_t t_row = tmem_addr(tmem, (warp & 3) * 32, C::kColS + stage * 128);
@@ -739,8 +750,10 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
           // batches of kBatch pairs: all scaled inputs, then all exponentials back to
           // back (so the MUFU latency of one is hidden behind the issue of the next),
           // then the sums and the bf16 packing
+          constexpr int kPairsLast = (128 - kHelperCols<D, kCausal || kRagged> - 64) / 2;   // pairs of the third chunk: 16, or 8 at D = 64
 #pragma unroll
           for (int b = 0; b < 16; b += kBatch) {
+            if (c == 2 && b >= kPairsLast) break;
             float2 x[kBatch], e[kBatch];
 #pragma unroll
             for (int i = 0; i < kBatch; ++i)
@@ -761,7 +774,14 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
               pk[b + i] = pack_bf16x2(e[i].x, e[i].y);
             }
           }
-          tmem_st16(t_row + c * 16, pk);
+          if (c == 2 && kPairsLast == 8) {
+            uint32_t pk8[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) pk8[i] = pk[i];
+            tmem_st8(t_row + 32, pk8);
+          } else {
+            tmem_st16(t_row + c * 16, pk);
+          }
           if (c == 1 || c == kSoftmaxChunks - 1) {
             // this warp's share of a 64-column half of P is in tensor memory: publish it
             tc_wait_st();
@@ -787,7 +807,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
     // =====================================================================
     // 104 registers is below the 128 the kernel launches with: a release, like the
     // MMA/load warpgroup's, that the two softmax warpgroups' increase draws on
-    setmaxnreg_dec<kRegsCorrection>();
+    setmaxnreg_dec<(kHelperCols<D, kCausal || kRagged> == 48 ? kRegsCorrection64 : kRegsCorrection)>();
     const int row = tid & 127;
     const uint32_t t_lane = tmem_addr(tmem, (warp & 3) * 32, 0);
     mbar_arrive(bar(C::kBarPFull + 0));   // O is free for the first item
@@ -808,6 +828,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
         for (int s = 0; s < 2; ++s) {
           if (j < nt[s]) {
             uint32_t sv[32];
+            [[maybe_unused]] uint32_t sw[16];   // head dim 64: key columns 80..95 as well
             // Only a stage's last tile can hold masked keys: those above the diagonal
             // (causal) or past the end of the sequence (non-causal, S % 128 != 0). `keep`
             // is the last key column this row keeps there.
@@ -820,7 +841,9 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
               mbar_wait(bar(C::kBarSFull + s), cnt_h[s] & 1u, wctx, kSiteSoftmaxSFull);
               ++cnt_h[s];
               tc_fence_after();
+              if (kHelperCols<D, kCausal || kRagged> == 48) tmem_ld16(t_lane + C::kColS + s * 128 + 80, sw);
               tmem_ld32(t_lane + C::kColS + s * 128 + 96, sv);
+              if (kHelperCols<D, kCausal || kRagged> == 48) tc_wait_ld_bind16(sw);
               tc_wait_ld_bind(sv);
             }
             mbar_wait(bar(C::kBarAlpha + s), cnt_a[s] & 1u, wctx, kSiteCorrAlpha);
@@ -852,9 +875,23 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
               const float2 neg2 = make_float2(neg, neg);
               float2 sum2 = make_float2(0.0f, 0.0f);
               uint32_t pk[16];
+              [[maybe_unused]] uint32_t pk8[8];
               // two copies of the loop, so that the tiles without masked keys (all but one
               // per stage) carry no per-element compares
               auto exps = [&](auto masked) {
+                if (kHelperCols<D, kCausal || kRagged> == 48) {
+#pragma unroll
+                  for (int i = 0; i < 8; ++i) {
+                    float2 e = exp2_poly2(__ffma2_rn(
+                        make_float2(__uint_as_float(sw[2 * i]), __uint_as_float(sw[2 * i + 1])), scale2, neg2));
+                    if (decltype(masked)::value) {
+                      if (80 + 2 * i > keep) e.x = 0.0f;
+                      if (80 + 2 * i + 1 > keep) e.y = 0.0f;
+                    }
+                    sum2 = __fadd2_rn(sum2, e);
+                    pk8[i] = pack_bf16x2(e.x, e.y);
+                  }
+                }
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
                   float2 e = exp2_poly2(__ffma2_rn(
@@ -869,6 +906,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
                 }
               };
               if (mask_tile) exps(BoolTag<true>{}); else exps(BoolTag<false>{});
+              if (kHelperCols<D, kCausal || kRagged> == 48) tmem_st8(t_lane + C::kColS + s * 128 + 40, pk8);   // P columns of keys 80..95
               tmem_st16(t_lane + C::kColS + s * 128 + 48, pk);   // P columns of keys 96..127
               tc_wait_st();
               tc_fence_before();
