@@ -25,7 +25,12 @@
 //     an MMA issue that waited for the consumer's previous arrival, so no padding
 //     commits and no split-by-parity barriers are needed; across items, where a
 //     stage may run a short item ahead, the row sums are handed over through l_free;
-//   * every wait is bounded and reports to a status word.
+//   * every wait is bounded and reports to a status word;
+//   * where whole items dealt round robin would leave SMs idle through the last round
+//     (fewer items than SMs, long sequences), that round is cut along the key axis into
+//     equal shares for all SMs; the pieces of an item meet unnormalised in per-CTA scratch
+//     slots and are merged by the log-sum-exp rule in the CTA that holds the item's first
+//     keys (attn_sched.cuh, the kTail instantiations of the kernel, plan_schedule below).
 //
 // Roles (512 threads): warps 0-3 / 4-7 softmax of stage 0 / 1 (thread = one row),
 // warps 8-11 correction (O rescale, their share of the exponentials, epilogue),
