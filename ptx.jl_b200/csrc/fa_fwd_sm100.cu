@@ -82,9 +82,9 @@ static_assert(256 * kRegsSoftmax + 128 * kRegsCorrection + 128 * kRegsOther <= 6
 constexpr int kRegsSoftmax64 = 160, kRegsCorrection64 = 120;
 static_assert(256 * kRegsSoftmax64 + 128 * kRegsCorrection64 + 128 * kRegsOther <= 65536,
               "register re-split must fit the register file");
-// (only in the kernel without masking code: the causal and the ragged-length kernels
-// measured a quarter to a third slower with it at head dim 64)
-template <int D, bool kMasks> constexpr int kHelperCols = (D == 64 && !kMasks) ? 48 : 32;   // key columns per tile on the correction warps
+// (only in the plain kernel: the causal and the ragged-length kernels measured a quarter to a
+// third slower with it at head dim 64, and the kernels with a cut last round spill with it)
+template <int D, bool kOther> constexpr int kHelperCols = (D == 64 && !kOther) ? 48 : 32;   // key columns per tile on the correction warps
 
 // Which of the 16 element pairs of every 32-column chunk take the FMA-pipe
 // polynomial exp2 instead of the MUFU ex2 (bit i = pair i). The MUFU pipe
@@ -668,7 +668,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
     // softmax: warpgroup `stage` owns the 128 rows of that stage; one row
     // per thread, the whole 128-column tile of scores in registers.
     // =====================================================================
-    setmaxnreg_inc<(kHelperCols<D, kCausal || kRagged> == 48 ? kRegsSoftmax64 : kRegsSoftmax)>();
+    setmaxnreg_inc<(kHelperCols<D, kCausal || kRagged || kTail> == 48 ? kRegsSoftmax64 : kRegsSoftmax)>();
     const int stage = warp >> 2;
     const int row = tid & 127;
     const uint32_t t_row = tmem_addr(tmem, (warp & 3) * 32, C::kColS + stage * 128);
@@ -755,7 +755,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
           // batches of kBatch pairs: all scaled inputs, then all exponentials back to
           // back (so the MUFU latency of one is hidden behind the issue of the next),
           // then the sums and the bf16 packing
-          constexpr int kPairsLast = (128 - kHelperCols<D, kCausal || kRagged> - 64) / 2;   // pairs of the third chunk: 16, or 8 at D = 64
+          constexpr int kPairsLast = (128 - kHelperCols<D, kCausal || kRagged || kTail> - 64) / 2;   // pairs of the third chunk: 16, or 8 at D = 64
 #pragma unroll
           for (int b = 0; b < 16; b += kBatch) {
             if (c == 2 && b >= kPairsLast) break;
@@ -812,7 +812,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
     // =====================================================================
     // 104 registers is below the 128 the kernel launches with: a release, like the
     // MMA/load warpgroup's, that the two softmax warpgroups' increase draws on
-    setmaxnreg_dec<(kHelperCols<D, kCausal || kRagged> == 48 ? kRegsCorrection64 : kRegsCorrection)>();
+    setmaxnreg_dec<(kHelperCols<D, kCausal || kRagged || kTail> == 48 ? kRegsCorrection64 : kRegsCorrection)>();
     const int row = tid & 127;
     const uint32_t t_lane = tmem_addr(tmem, (warp & 3) * 32, 0);
     mbar_arrive(bar(C::kBarPFull + 0));   // O is free for the first item
@@ -846,9 +846,9 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
               mbar_wait(bar(C::kBarSFull + s), cnt_h[s] & 1u, wctx, kSiteSoftmaxSFull);
               ++cnt_h[s];
               tc_fence_after();
-              if (kHelperCols<D, kCausal || kRagged> == 48) tmem_ld16(t_lane + C::kColS + s * 128 + 80, sw);
+              if (kHelperCols<D, kCausal || kRagged || kTail> == 48) tmem_ld16(t_lane + C::kColS + s * 128 + 80, sw);
               tmem_ld32(t_lane + C::kColS + s * 128 + 96, sv);
-              if (kHelperCols<D, kCausal || kRagged> == 48) tc_wait_ld_bind16(sw);
+              if (kHelperCols<D, kCausal || kRagged || kTail> == 48) tc_wait_ld_bind16(sw);
               tc_wait_ld_bind(sv);
             }
             mbar_wait(bar(C::kBarAlpha + s), cnt_a[s] & 1u, wctx, kSiteCorrAlpha);
@@ -884,7 +884,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
               // two copies of the loop, so that the tiles without masked keys (all but one
               // per stage) carry no per-element compares
               auto exps = [&](auto masked) {
-                if (kHelperCols<D, kCausal || kRagged> == 48) {
+                if (kHelperCols<D, kCausal || kRagged || kTail> == 48) {
 #pragma unroll
                   for (int i = 0; i < 8; ++i) {
                     float2 e = exp2_poly2(__ffma2_rn(
@@ -911,7 +911,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
                 }
               };
               if (mask_tile) exps(BoolTag<true>{}); else exps(BoolTag<false>{});
-              if (kHelperCols<D, kCausal || kRagged> == 48) tmem_st8(t_lane + C::kColS + s * 128 + 40, pk8);   // P columns of keys 80..95
+              if (kHelperCols<D, kCausal || kRagged || kTail> == 48) tmem_st8(t_lane + C::kColS + s * 128 + 40, pk8);   // P columns of keys 80..95
               tmem_st16(t_lane + C::kColS + s * 128 + 48, pk);   // P columns of keys 96..127
               tc_wait_st();
               tc_fence_before();
