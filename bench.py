@@ -491,10 +491,13 @@ def run_native_arm(args):
     ms_per_step = head["ms"]
     value = prob.work * world / (ms_per_step * 1e-3) / unit_scale
     achieved = prob.work / (ms_per_step * 1e-3) / unit_scale   # one launch on one GPU
-    region_ms = ms_per_step * args.steps
+    # launches run back to back from the warm-up to the last region: a quarter of a second of
+    # that puts the GPU under its power cap, where the sustained cuBLAS figure is the fair peak
+    busy_ms = ms_per_step * (head["warmup_launches"] + head["steps"] * head["repeats"])
     if bound == "tensor":
-        peak = peak_sustained if region_ms >= 500.0 else peak_burst
-        peak_text = f"{peak_kind} ({'sustained' if region_ms >= 500.0 else 'burst'} cuBLAS bf16)"
+        long_run = busy_ms >= 250.0
+        peak = peak_sustained if long_run else peak_burst
+        peak_text = f"{peak_kind} ({'sustained' if long_run else 'burst'} cuBLAS bf16)"
     else:
         peak, peak_text = peak_hbm, f"{peak_kind} (copy)"
 
@@ -731,8 +734,8 @@ def run_native_arm(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
-    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["native", "reference"], default="native")
     ap.add_argument("--workload", choices=sorted(WORKLOADS) + sorted(GEMM_WORKLOADS) + sorted(ROWWISE_WORKLOADS),
                     default="c2")
