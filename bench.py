@@ -14,7 +14,9 @@ per GPU, launched by torch.distributed.run.
 Prints ONE JSON line on rank 0. `value` is whole-job TFLOPS with inputs resident
 in HBM, timed with CUDA events on the launching stream, max over ranks. `e2e` is
 the same metric through the library call with HOST buffers: pinned host -> device
-copies of Q, K, V and the device -> host copy of O inside the timed region.
+copies of Q, K, V and the device -> host copy of O inside the timed region;
+`e2e.grouped_kv` repeats it with K and V shared by groups of four query heads
+(same flops, half the bytes in).
 """
 from __future__ import annotations
 
@@ -615,50 +617,79 @@ def run_native_arm(args):
     inputs, o = prob.inputs, prob.out
     e2e_steps = max(3, min(args.steps, 10))
     nbuf = 3
-    h_in = [[torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in inputs] for _ in range(nbuf)]
-    h_out = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for _ in range(nbuf)]
-    for b in range(nbuf):
-        for h, t in zip(h_in[b], inputs):
-            h.copy_(t)
-    d_in = [[torch.empty_like(t) for t in inputs] for _ in range(nbuf)]
-    d_out = [torch.empty_like(o) for _ in range(nbuf)]
-    s_in, s_cmp, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
-    ev_in = [torch.cuda.Event() for _ in range(nbuf)]
-    ev_cmp = [torch.cuda.Event() for _ in range(nbuf)]
-    ev_out = [torch.cuda.Event() for _ in range(nbuf)]
 
-    def e2e_loop(n):
-        # three streams, three buffer sets: the copy-in of the next steps and the copy-out of
-        # the previous one overlap the kernel of step i
-        for i in range(n):
-            b = i % nbuf
-            with torch.cuda.stream(s_in):
-                s_in.wait_event(ev_cmp[b])          # device inputs of slot b no longer in use
-                for d, h in zip(d_in[b], h_in[b]):
-                    d.copy_(h, non_blocking=True)
-                ev_in[b].record(s_in)
-            with torch.cuda.stream(s_cmp):
-                s_cmp.wait_event(ev_in[b])
-                s_cmp.wait_event(ev_out[b])         # device output of slot b already copied out
-                prob.run(d_in[b], d_out[b], stream=s_cmp)
-                ev_cmp[b].record(s_cmp)
-            with torch.cuda.stream(s_out):
-                s_out.wait_event(ev_cmp[b])
-                h_out[b].copy_(d_out[b], non_blocking=True)
-                ev_out[b].record(s_out)
+    def e2e_measure(ins, want):
+        """`e2e_steps` steps of: pinned host inputs -> device, the launch, device output ->
+        pinned host; three streams and `nbuf` buffer sets, so the copy-in of the next steps and
+        the copy-out of the previous one overlap the kernel of step i. Returns (ms per step, max
+        over ranks; whether the last host output equals `want`, the resident run's output)."""
+        h_in = [[torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in ins] for _ in range(nbuf)]
+        h_out = [torch.empty(want.shape, dtype=want.dtype).pin_memory() for _ in range(nbuf)]
+        for b in range(nbuf):
+            for h, t in zip(h_in[b], ins):
+                h.copy_(t)
+        d_in = [[torch.empty_like(t) for t in ins] for _ in range(nbuf)]
+        d_out = [torch.empty_like(want) for _ in range(nbuf)]
+        s_in, s_cmp, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
+        ev_in = [torch.cuda.Event() for _ in range(nbuf)]
+        ev_cmp = [torch.cuda.Event() for _ in range(nbuf)]
+        ev_out = [torch.cuda.Event() for _ in range(nbuf)]
 
-    e2e_loop(nbuf)
-    bench.barrier()
-    t0 = time.perf_counter()
-    e2e_loop(e2e_steps)
-    torch.cuda.synchronize()
-    e2e_ms_local = (time.perf_counter() - t0) * 1e3
-    e2e_ms_step = bench.max_over_ranks(e2e_ms_local) / e2e_steps
+        def loop(n):
+            for i in range(n):
+                b = i % nbuf
+                with torch.cuda.stream(s_in):
+                    s_in.wait_event(ev_cmp[b])          # device inputs of slot b no longer in use
+                    for d, h in zip(d_in[b], h_in[b]):
+                        d.copy_(h, non_blocking=True)
+                    ev_in[b].record(s_in)
+                with torch.cuda.stream(s_cmp):
+                    s_cmp.wait_event(ev_in[b])
+                    s_cmp.wait_event(ev_out[b])         # device output of slot b already copied out
+                    prob.run(d_in[b], d_out[b], stream=s_cmp)
+                    ev_cmp[b].record(s_cmp)
+                with torch.cuda.stream(s_out):
+                    s_out.wait_event(ev_cmp[b])
+                    h_out[b].copy_(d_out[b], non_blocking=True)
+                    ev_out[b].record(s_out)
+
+        loop(nbuf)
+        bench.barrier()
+        t0 = time.perf_counter()
+        loop(e2e_steps)
+        torch.cuda.synchronize()
+        ms_local = (time.perf_counter() - t0) * 1e3
+        ms_step = bench.max_over_ranks(ms_local) / e2e_steps
+        same = bool(torch.equal(h_out[(e2e_steps - 1) % nbuf].to(dev), want))
+        return ms_step, same
+
+    def nbytes(ts):
+        return sum(t.numel() * t.element_size() for t in ts)
+
+    e2e_ms_step, e2e_ok = e2e_measure(inputs, o)
     e2e_value = prob.work * world / (e2e_ms_step * 1e-3) / unit_scale
-    e2e_ok = bool(torch.equal(h_out[(e2e_steps - 1) % nbuf].to(dev), o))
-    h2d_bytes = sum(t.numel() * t.element_size() for t in inputs)
-    d2h_bytes = o.numel() * o.element_size()
+    h2d_bytes = nbytes(inputs)
+    d2h_bytes = nbytes([o])
     check_status("the end-to-end region")
+
+    # the same call with K and V shared by groups of four query heads (the entry point's
+    # grouped-head form): the same flops from half the bytes over PCIe
+    e2e_grouped = None
+    if args.workload in WORKLOADS and not args.headline_only:
+        q, k, v = inputs
+        group = 4
+        kg, vg = (t[:, : t.shape[1] // group].contiguous() for t in (k, v))
+        o_g = torch.empty_like(o)
+        prob.run([q, kg, vg], o_g)
+        torch.cuda.synchronize()
+        g_ms, g_ok = e2e_measure([q, kg, vg], o_g)
+        check_status("the grouped-head end-to-end region")
+        g_h2d = nbytes([q, kg, vg])
+        e2e_grouped = {"kv_heads": int(kg.shape[1]), "query_heads": int(q.shape[1]),
+                       "value": prob.work * world / (g_ms * 1e-3) / unit_scale, "unit": unit,
+                       "ms_per_step": g_ms, "h2d_bytes_per_step": g_h2d, "d2h_bytes_per_step": d2h_bytes,
+                       "h2d_gbs_per_rank": g_h2d / (g_ms * 1e-3) / 1e9, "matches_resident_run": g_ok}
+        del kg, vg, o_g
 
     # verification checksum gathered over ranks (outside every timed region)
     cs = torch.tensor([float(o.float().sum()), float(o.float().abs().sum())], dtype=torch.float64, device=dev)
@@ -690,11 +721,14 @@ def run_native_arm(args):
                     "h2d_gbs_per_rank": h2d_bytes / (e2e_ms_step * 1e-3) / 1e9,
                     "h2d_gbs_all_ranks": world * h2d_bytes / (e2e_ms_step * 1e-3) / 1e9,
                     "buffer_sets": nbuf,
+                    "d2h_gbs_per_rank": d2h_bytes / (e2e_ms_step * 1e-3) / 1e9,
                     "matches_resident_run": e2e_ok, "rank0_gpu_local_cpus": local_cpus},
             "gpu_launches": args.steps,
             "clocks": head["clocks"],
             "checksum": {"sum": float(cs[0]), "abs_sum": float(cs[1])},
         }
+        if e2e_grouped is not None:
+            line["e2e"]["grouped_kv"] = e2e_grouped
         if sustained is not None:
             line["sustained"] = sustained
         if configs:
