@@ -51,7 +51,7 @@ ROWWISE_WORKLOADS = {"softmax": (65536, 4096, 20260011), "rms_norm": (65536, 409
 # profiles/gemm_bf16_c5.md.
 # (softmax: captured at rows = 16384 and scaled by 4 to the bench's 65536 rows, every row being
 # read and written once: profiles/rowwise_softmax_n4096.md)
-NCU_TRAFFIC_BYTES = {"c2": 201.44e6 + 43.03e6, "c3": 201.38e6 + 45.59e6, "c4": 1649.54e6 + 517.57e6,
+NCU_TRAFFIC_BYTES = {"c2": 201.44e6 + 43.03e6, "c3": 201.39e6 + 45.83e6, "c4": 1649.54e6 + 517.57e6,
                      "c5": 1067.3e6 + 131.1e6,
                      "softmax": 4 * (268.45e6 + 218.52e6)}
 FALLBACK_PEAK_TFLOPS = 1590.0
@@ -700,7 +700,7 @@ def run_native_arm(args):
     if rank == 0:
         line = {
             "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
-            "warmup": head["warmup_launches"], "ms_per_step": ms_per_step, "higher_is_better": True,
+            "warmup": args.warmup, "warmup_launches": head["warmup_launches"], "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16" if bound == "tensor" else "f32", "data": "synthetic",
             "config": {"workload": f"{prob.text} per GPU, {shard_text}",
                        "l2": f"inputs+output {prob.algo_bytes >> 20} MiB per launch > 126 MB L2, no explicit flush",
