@@ -100,8 +100,8 @@ def rowwise_cpu_sample(workload, sample_rows):
 
 
 class ClockSampler(threading.Thread):
-    """Samples the SM clock (every ~0.3 ms) and the throttle reasons (every 8th sample)
-    through NVML for the life of the run; each sample carries its host time, so any timed
+    """Samples the SM clock (every ~0.3 ms) and the throttle reasons and board power (every
+    8th sample) through NVML for the life of the run; each sample carries its host time, so any timed
     region can ask for the clocks it saw. Reads only: no GPU setting is changed."""
 
     def __init__(self, index):
@@ -110,7 +110,9 @@ class ClockSampler(threading.Thread):
         self.t = []          # perf_counter of each sample
         self.mhz = []
         self.reason_log = []  # (perf_counter, frozenset of active reasons)
+        self.power_log = []   # (perf_counter, board power in watts)
         self.max_mhz = None
+        self.power_limit_w = None
         self.error = None
         self._stop_evt = threading.Event()
 
@@ -120,6 +122,10 @@ class ClockSampler(threading.Thread):
             nv.nvmlInit()
             h = nv.nvmlDeviceGetHandleByIndex(self.index)
             self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+            try:
+                self.power_limit_w = nv.nvmlDeviceGetEnforcedPowerLimit(h) / 1000.0
+            except Exception:
+                self.power_limit_w = None
             names = {
                 "hw_slowdown": nv.nvmlClocksEventReasonHwSlowdown,
                 "hw_thermal_slowdown": nv.nvmlClocksEventReasonHwThermalSlowdown,
@@ -133,6 +139,10 @@ class ClockSampler(threading.Thread):
                 if i % 8 == 0:
                     r = nv.nvmlDeviceGetCurrentClocksEventReasons(h)
                     self.reason_log.append((self.t[-1], frozenset(k for k, bit in names.items() if r & bit)))
+                    try:
+                        self.power_log.append((self.t[-1], nv.nvmlDeviceGetPowerUsage(h) / 1000.0))
+                    except Exception:
+                        pass
                 i += 1
                 time.sleep(0.0003)
         except Exception as e:  # NVML missing: report that instead of inventing numbers
@@ -151,9 +161,12 @@ class ClockSampler(threading.Thread):
                 reasons |= rs
         if self.error:
             reasons.add(self.error)
+        watts = [w for t, w in list(self.power_log) if t0 <= t <= t1]
         return {"sm_mhz": statistics.median(vals) if vals else None,
                 "sm_mhz_min": min(vals) if vals else None, "sm_max_mhz": self.max_mhz,
-                "samples": len(vals), "reasons": sorted(reasons)}
+                "samples": len(vals), "reasons": sorted(reasons),
+                "power_w": statistics.median(watts) if watts else None,
+                "power_w_max": max(watts) if watts else None, "power_limit_w": self.power_limit_w}
 
 
 def physical_gpu_index(local_rank):
@@ -526,6 +539,17 @@ def run_native_arm(args):
                              "steps": steps_n, "repeats": 3, "sm_mhz": full_t["clocks"]["sm_mhz"],
                              "kcycles_per_launch": (full_t["ms"] * full_t["clocks"]["sm_mhz"]
                                                     if full_t["clocks"]["sm_mhz"] else None)}
+            configs[name]["power_w"] = full_t["clocks"].get("power_w")
+            if is_gemm:
+                # the vendor library on the same operands, same box, same moment: what the measured
+                # peak looks like today (library code: measured beside the product, never on its path)
+                a_op, bt_op = full.inputs
+                lib_out = torch.empty_like(full.out)
+                lib_t = bench.measure(lambda: torch.matmul(a_op, bt_op.t(), out=lib_out), steps_n, 3, repeats=3)
+                configs[name]["cublas_same_run"] = {
+                    "ms": lib_t["ms"], "tflops": full.work / (lib_t["ms"] * 1e-3) / 1e12,
+                    "sm_mhz": lib_t["clocks"]["sm_mhz"], "power_w": lib_t["clocks"].get("power_w")}
+                del lib_out
             if name == "c3":
                 # at D = 64 the exponentials, not the tensor pipe, bound a tile: 16 ex2/clk/SM on the
                 # MUFU (measured: profiles/ex2_throughput.md) against 2*D flop per score on the tensor pipe
